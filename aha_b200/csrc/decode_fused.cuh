@@ -6,7 +6,7 @@
 // the whole step:
 //   * the last warp (one elected lane) is the PRODUCER: it walks this CTA's static schedule of transfers for all
 //     layers -- weight row slabs and paged-KV half pages -- and issues TMA bulk copies
-//     (cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes, SASS UBLKCP, L2 evict-first policy) into
+//     (cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes, L2 evict-first policy) into
 //     a ring of 16 KB shared-memory stages guarded by full/empty mbarriers.  It never waits for activations, so
 //     weights for the next phases keep streaming while the consumers sit in a grid barrier;
 //   * the other 11 warps are CONSUMERS: per phase they stage the activation vector in shared memory (RMSNorm
