@@ -46,6 +46,10 @@ class BatchRequest(C.Structure):
     _fields_ = [("ids", C.POINTER(C.c_uint32)), ("seq_len", C.c_size_t), ("mm", C.POINTER(MM)), ("params", GenParams)]
 
 
+class FeedEntry(C.Structure):
+    _fields_ = [("slot", C.c_int32), ("ids", C.POINTER(C.c_uint32)), ("n", C.c_size_t), ("want", C.POINTER(C.c_int32)), ("n_want", C.c_size_t)]
+
+
 class Usage(C.Structure):
     _fields_ = [("prompt_tokens", C.c_uint32), ("completion_tokens", C.c_uint32), ("prompt_secs", C.c_double),
                 ("completion_secs", C.c_double), ("vision_secs", C.c_double)]
@@ -80,6 +84,10 @@ SYMBOLS = {
     "aha_b200_batch_add": (C.c_int, [_P, C.POINTER(BatchRequest), C.POINTER(C.c_int32), _U32P, C.POINTER(C.c_int32), C.POINTER(Usage)]),
     "aha_b200_batch_step": (C.c_int, [_P, _U32P, C.POINTER(C.c_int32), C.POINTER(C.c_size_t)]),
     "aha_b200_batch_close": (C.c_int, [_P]),
+    "aha_b200_seq_open": (C.c_int, [_P, C.POINTER(C.c_int32)]),
+    "aha_b200_seq_close": (C.c_int, [_P, C.c_int32]),
+    "aha_b200_seq_feed": (C.c_int, [_P, C.POINTER(FeedEntry), C.c_size_t, _F32P, C.c_size_t]),
+    "aha_b200_seq_info": (C.c_int, [_P, C.c_int32, C.POINTER(C.c_int64), C.POINTER(C.c_int64), C.POINTER(C.c_int32)]),
     "aha_b200_generate_stream": (C.c_int, [_P, _U32P, C.c_size_t, C.POINTER(MM), C.POINTER(GenParams), TOKEN_CALLBACK, C.c_void_p,
                                            C.POINTER(Usage)]),
     "aha_b200_asr_generate": (C.c_int, [_P, C.POINTER(AsrChunk), C.c_size_t, C.POINTER(GenParams), _U32P, C.c_size_t,

@@ -11,6 +11,7 @@
 
 #include "audio_model.cuh"
 #include "preprocess.cuh"
+#include "seq_engine.h"
 #include "text_model.cuh"
 #include "batch_decode.cuh"
 #include "vision_model.cuh"
@@ -23,7 +24,7 @@ std::string g_create_error;
 }  // namespace
 
 struct aha_model {
-    enum Kind { QWEN3, QWEN3VL, QWEN3_ASR } kind = QWEN3;
+    enum Kind { QWEN3, QWEN3VL, QWEN3_ASR, LAYERED } kind = QWEN3;
     Ctx ctx;
     TextModel text;
     VisionModel vision;
@@ -49,6 +50,10 @@ struct aha_model {
     std::vector<uint32_t> cached_ids;   // tokens whose K/V occupy positions 0 .. n-1 of the paged cache
     uint64_t cached_mm_fp = 0;          // fingerprint of the multimodal tensors those tokens were embedded with (0 = none)
     size_t last_prefix_hit = 0;         // tokens the last generate call did not have to prefill
+    // Layered sequence engine (seq_engine.h): models whose config.json lists their layers.  It replaces `text` for those handles; the entry points
+    // below route to it.  seq_single: the slot the single-request entries (forward_initial / _step / _extend) work on.
+    std::unique_ptr<SeqEngine> seq;
+    int seq_single = -1;
     BatchDecoder batch;                 // several sequences decoded in lockstep (aha_b200_generate_batch); buffers allocated on first use
     // Continuous batching (aha_b200_batch_open / _add / _step / _close): requests join and leave a running batch between steps
     struct BatchSession {
@@ -278,6 +283,44 @@ std::vector<uint32_t> mm_token_ids(const aha_model* m) {
     for (int v : {m->image_token_id, m->video_token_id, m->audio_token_id}) if (v >= 0) t.push_back((uint32_t)v);
     return t;
 }
+// ---- handles served by the layered sequence engine (seq_engine.h)
+bool is_seq(const aha_model* m) { return m->kind == aha_model::LAYERED; }
+void require_text(const aha_model* m, const char* what) {
+    AHA_REQUIRE(!is_seq(m), std::string(what) + " is not available on a layered-engine handle");
+}
+uint32_t host_argmax(const float* lg, int V) {   // first maximal index, like the device ArgMax
+    int bi = 0;
+    for (int i = 1; i < V; ++i) if (lg[i] > lg[bi]) bi = i;
+    return (uint32_t)bi;
+}
+void seq_drop(aha_model* m) {
+    AHA_CUDA_CHECK(cudaStreamSynchronize(m->ctx.stream));
+    m->seq->release_all();
+    m->seq_single = -1;
+    m->session = aha_model::BatchSession{};
+}
+// forward_initial / forward_step / forward_extend: one sequence in slot seq_single, logits of the LAST token
+void seq_forward(aha_model* m, const uint32_t* ids, size_t S, size_t offset, bool initial, float* logits_out, uint32_t* argmax_out) {
+    SeqEngine& E = *m->seq;
+    AHA_REQUIRE(ids != nullptr && S >= 1, "input_ids must hold at least one token");
+    if (initial) {
+        AHA_REQUIRE(offset == 0, "forward_initial starts a sequence: seqlen_offset must be 0");
+        if (m->seq_single >= 0 && E.live(m->seq_single)) E.release(m->seq_single);
+        m->seq_single = E.admit();
+    } else {
+        AHA_REQUIRE(m->seq_single >= 0 && E.live(m->seq_single), "no sequence is open: call forward_initial first");
+        AHA_REQUIRE((size_t)E.position(m->seq_single) == offset, "seqlen_offset does not match the tokens the sequence holds (a recurrent state cannot be rewound)");
+    }
+    const int32_t want = (int32_t)S - 1;
+    SeqStepEntry e;
+    e.slot = m->seq_single; e.tokens = ids; e.n = (int)S; e.want = &want; e.n_want = 1;
+    std::vector<float> tmp;
+    float* lg = logits_out;
+    if (!lg) { tmp.resize(E.vocab()); lg = tmp.data(); }
+    E.step(&e, 1, lg, nullptr);
+    if (argmax_out) *argmax_out = host_argmax(lg, E.vocab());
+}
+
 void require_no_session(aha_model* m) {
     AHA_REQUIRE(!m->session.open, "a batch session is open on this handle: call aha_b200_batch_close first");
 }
@@ -524,8 +567,26 @@ int aha_b200_create(const char* kind, const char* config_json, const aha_tensor_
             m->text.load(m->ctx, tc, wt, "thinker.model.", "thinker.lm_head.weight", tp_rank, tp_world);
             m->audio.load(m->ctx, AudioCfg::from_json(tk.at("audio_config")), wt, "thinker.audio_tower.", o.max_frames > 0 ? o.max_frames : 3000);
             AHA_REQUIRE(m->audio.cfg.out_dim == tc.H, "audio output_dim must equal the text hidden_size");
+        } else if (k == "malasun" || k == "layered") {
+            // a model that is a list of layers (config.json "layers"); reserved[1] = 1: exact fp32 mode, reserved[2]: sequence slots (0 = 8)
+            AHA_REQUIRE(tp_world == 1, "the layered engine is single-GPU");
+            m->kind = aha_model::LAYERED;
+            SeqEngineOptions so;
+            so.max_tokens = max_ctx;
+            so.max_seqs = o.reserved[2] > 0 ? std::min<int>(o.reserved[2], kGemvBatchMax) : kGemvBatchMax;
+            so.max_step_tokens = o.max_prefill > 0 ? o.max_prefill : std::min(max_ctx, 2048);
+            so.fp32 = o.reserved[1] == 1;
+            so.use_graph = o.use_graph != 0;
+            so.gemm_impl = o.gemm_impl;
+            m->seq.reset(make_layered_engine(m->ctx, root, wt, so));
         } else {
-            throw std::runtime_error("unknown model kind '" + k + "' (expected qwen3 | qwen3vl | qwen3_asr)");
+            throw std::runtime_error("unknown model kind '" + k + "' (expected qwen3 | qwen3vl | qwen3_asr | malasun)");
+        }
+        if (m->kind == aha_model::LAYERED) {
+            for (size_t i = 0; i < n_eos; ++i) m->stop_ids.push_back(eos_ids[i]);
+            AHA_CUDA_CHECK(cudaDeviceSynchronize());
+            *out = m;
+            return 0;
         }
         m->text.alloc_runtime(max_ctx, max_prefill, o.use_graph != 0, o.decode_impl);
         m->text.init_tp(o.tp_comm);
@@ -550,15 +611,15 @@ int aha_b200_create(const char* kind, const char* config_json, const aha_tensor_
 
 int aha_b200_forward_initial(aha_model* m, const uint32_t* ids, size_t seq_len, size_t seqlen_offset, const aha_mm* mm, float* logits_out,
                              uint32_t* argmax_out) {
-    return guarded(m, [&] { require_no_session(m); m->cached_ids.clear(); forward_any(m, ids, seq_len, seqlen_offset, mm, true, logits_out, argmax_out); });
+    return guarded(m, [&] { require_no_session(m); if (is_seq(m)) { seq_forward(m, ids, seq_len, seqlen_offset, true, logits_out, argmax_out); return; } m->cached_ids.clear(); forward_any(m, ids, seq_len, seqlen_offset, mm, true, logits_out, argmax_out); });
 }
 
 int aha_b200_forward_step(aha_model* m, const uint32_t* ids, size_t seq_len, size_t seqlen_offset, float* logits_out, uint32_t* argmax_out) {
-    return guarded(m, [&] { require_no_session(m); m->cached_ids.clear(); forward_any(m, ids, seq_len, seqlen_offset, nullptr, false, logits_out, argmax_out); });
+    return guarded(m, [&] { require_no_session(m); if (is_seq(m)) { seq_forward(m, ids, seq_len, seqlen_offset, false, logits_out, argmax_out); return; } m->cached_ids.clear(); forward_any(m, ids, seq_len, seqlen_offset, nullptr, false, logits_out, argmax_out); });
 }
 
 int aha_b200_forward_extend(aha_model* m, const uint32_t* ids, size_t seq_len, size_t seqlen_offset, float* logits_out, uint32_t* argmax_out) {
-    return guarded(m, [&] { require_no_session(m); m->cached_ids.clear(); forward_any(m, ids, seq_len, seqlen_offset, nullptr, false, logits_out, argmax_out, true); });
+    return guarded(m, [&] { require_no_session(m); if (is_seq(m)) { seq_forward(m, ids, seq_len, seqlen_offset, false, logits_out, argmax_out); return; } m->cached_ids.clear(); forward_any(m, ids, seq_len, seqlen_offset, nullptr, false, logits_out, argmax_out, true); });
 }
 
 size_t aha_b200_last_prefix_hit(aha_model* m) { return m ? m->last_prefix_hit : 0; }
@@ -573,6 +634,7 @@ uint64_t aha_b200_mm_fingerprint(const aha_mm* mm) { return mm_fingerprint(mm); 
 
 int aha_b200_clear_cache(aha_model* m) {
     return guarded(m, [&] {
+        if (is_seq(m)) { seq_drop(m); return; }
         AHA_CUDA_CHECK(cudaStreamSynchronize(m->ctx.stream));
         if (m->session.open) {   // clear_cache ends a batch session too: every sequence's K/V is gone
             for (auto& sl : m->batch.slots) sl.mapped = 0;
@@ -592,15 +654,6 @@ size_t aha_b200_stop_token_ids(aha_model* m, uint32_t* out, size_t cap) {
 }
 
 namespace {
-
-// get_logit_processor (sample.rs:7-38): which Sampling the request's parameters select
-int sampling_mode(const aha_gen_params& p) {
-    const bool has_t = !(p.temperature < 1e-7f);
-    const bool has_k = p.top_k > 0, has_p = p.top_p > 0.f;
-    if (!has_t) return SAMPLE_ARGMAX;
-    if (!has_k) return has_p ? SAMPLE_TOPP : SAMPLE_ALL;
-    return has_p ? SAMPLE_TOPK_TOPP : SAMPLE_TOPK;
-}
 
 struct GenSink {   // receives every generated token in order; returns true to stop the request (client went away)
     std::function<bool(uint32_t token, size_t index)> push;
@@ -712,6 +765,135 @@ void generate_impl(aha_model* m, const uint32_t* ids, size_t seq_len, const aha_
 }  // namespace
 
 namespace {
+// ---- handles of the layered sequence engine (seq_engine.h) ---------------------------------------------------------------------------------
+// The same entry points, served by the engine's ragged step: a prompt is one entry with many tokens, a decode step one token per live sequence.
+// generate_generic's rules (first token never EOS-checked unless AHA_GEN_EOS_ON_FIRST, an EOS token is delivered and ends the request) on one slot;
+// the sampled token stays on the device and is fed back from there.
+void seq_generate(aha_model* m, const uint32_t* ids, size_t seq_len, const aha_gen_params& params, const GenSink& sink, aha_usage* usage) {
+    SeqEngine& E = *m->seq;
+    require_no_session(m);
+    AHA_REQUIRE(ids && seq_len >= 1, "input_ids must hold at least one token");
+    const size_t sample_len = std::max<size_t>(params.max_tokens, 1);
+    AHA_REQUIRE((params.flags & (AHA_GEN_CONTINUE_RNG | AHA_GEN_REUSE_PREFIX)) == 0, "CONTINUE_RNG / REUSE_PREFIX are not available on a layered-engine handle");
+    using clk = std::chrono::steady_clock;
+    const auto t0 = clk::now();
+    const int slot = E.admit();
+    struct Release { SeqEngine& E; int slot; ~Release() { if (E.live(slot)) E.release(slot); } } rel{E, slot};
+    E.set_sampler(slot, params);
+    auto is_eos = [&](uint32_t t) { for (uint32_t e : m->stop_ids) if (e == t) return true; return false; };
+    SeqStepEntry e;
+    e.slot = slot; e.tokens = ids; e.n = (int)seq_len; e.sample = true;
+    uint32_t tok = 0;
+    E.step(&e, 1, nullptr, &tok);
+    const auto t1 = clk::now();
+    size_t done = 1;
+    bool stop = sink.push(tok, 0) || ((params.flags & AHA_GEN_EOS_ON_FIRST) != 0 && is_eos(tok));
+    e.tokens = nullptr; e.n = 1;
+    while (done < sample_len && !stop) {
+        E.step(&e, 1, nullptr, &tok);
+        ++done;
+        stop = sink.push(tok, done - 1) || is_eos(tok);
+    }
+    const auto t2 = clk::now();
+    if (usage) {
+        usage->prompt_tokens += (uint32_t)seq_len; usage->completion_tokens += (uint32_t)done;
+        usage->prompt_secs += std::chrono::duration<double>(t1 - t0).count();
+        usage->completion_secs += std::chrono::duration<double>(t2 - t1).count();
+    }
+}
+
+// Batch session on the engine: batch_add admits a request and runs its prompt as one step; batch_step is ONE ragged step with the fed-back token of
+// every running request.  Slot ids are the engine's slots.
+void seq_session_open(aha_model* m) { require_no_session(m); seq_drop(m); m->session.open = true; }
+void seq_session_add(aha_model* m, const aha_batch_request& r, int* slot_out, uint32_t* first_token, int* finished, aha_usage* usage) {
+    SeqEngine& E = *m->seq;
+    AHA_REQUIRE(m->session.open, "no batch session is open (aha_b200_batch_open)");
+    AHA_REQUIRE(r.ids && r.seq_len >= 1, "batch_add: the request needs input_ids");
+    const size_t sample_len = std::max<size_t>(r.params.max_tokens, 1);
+    const size_t need = (r.seq_len + sample_len + E.page_tokens() - 1) / E.page_tokens() * E.page_tokens();
+    AHA_REQUIRE(need <= E.free_tokens(), "batch_add: the request needs " + std::to_string(need) + " tokens of KV capacity, " + std::to_string(E.free_tokens()) + " are free");
+    using clk = std::chrono::steady_clock;
+    const auto t0 = clk::now();
+    const int slot = E.admit();
+    struct Guard { SeqEngine& E; int slot; bool ok = false; ~Guard() { if (!ok && E.live(slot)) E.release(slot); } } guard{E, slot};
+    E.set_sampler(slot, r.params);
+    SeqStepEntry e;
+    e.slot = slot; e.tokens = r.ids; e.n = (int)r.seq_len; e.sample = true;
+    uint32_t tok = 0;
+    E.step(&e, 1, nullptr, &tok);
+    guard.ok = true;
+    m->session.used[slot] = true; m->session.budget[slot] = sample_len; m->session.produced[slot] = 1;
+    bool stop = sample_len == 1;
+    if ((r.params.flags & AHA_GEN_EOS_ON_FIRST) != 0) for (uint32_t s : m->stop_ids) if (s == tok) stop = true;
+    if (usage) { *usage = aha_usage{}; usage->prompt_tokens = (uint32_t)r.seq_len; usage->completion_tokens = 1; usage->prompt_secs = std::chrono::duration<double>(clk::now() - t0).count(); }
+    if (stop) { E.release(slot); m->session.used[slot] = false; }
+    *slot_out = slot; *first_token = tok; *finished = stop ? 1 : 0;
+}
+size_t seq_session_step(aha_model* m, uint32_t* tokens_out, int32_t* status_out) {
+    SeqEngine& E = *m->seq;
+    AHA_REQUIRE(m->session.open, "no batch session is open (aha_b200_batch_open)");
+    std::vector<SeqStepEntry> ents;
+    for (int i = 0; i < kGemvBatchMax; ++i) {
+        status_out[i] = 0; tokens_out[i] = 0;
+        if (m->session.used[i]) { SeqStepEntry e; e.slot = i; e.n = 1; e.sample = true; ents.push_back(e); }
+    }
+    if (ents.empty()) return 0;
+    std::vector<uint32_t> toks(ents.size());
+    E.step(ents.data(), (int)ents.size(), nullptr, toks.data());
+    for (size_t k = 0; k < ents.size(); ++k) {
+        const int slot = ents[k].slot;
+        tokens_out[slot] = toks[k];
+        m->session.produced[slot] += 1;
+        bool stop = m->session.produced[slot] >= m->session.budget[slot];
+        for (uint32_t s : m->stop_ids) if (s == toks[k]) stop = true;
+        status_out[slot] = stop ? 2 : 1;
+        if (stop) { E.release(slot); m->session.used[slot] = false; }
+    }
+    return ents.size();
+}
+// generate_batch: ALL prompts in one ragged step, then lockstep decode steps of the requests that go on
+void seq_generate_batch(aha_model* m, const aha_batch_request* reqs, size_t n, uint32_t* out_tokens, size_t cap, size_t* n_out, aha_usage* usage) {
+    SeqEngine& E = *m->seq;
+    require_no_session(m);
+    AHA_REQUIRE(n >= 1 && n <= (size_t)E.max_seqs(), "generate_batch: more requests than sequence slots");
+    seq_drop(m);
+    struct Reset { aha_model* m; ~Reset() { seq_drop(m); } } reset{m};
+    auto is_eos = [&](uint32_t t) { for (uint32_t e : m->stop_ids) if (e == t) return true; return false; };
+    std::vector<SeqStepEntry> ents(n);
+    std::vector<size_t> sample_len(n);
+    for (size_t i = 0; i < n; ++i) {
+        AHA_REQUIRE(reqs[i].ids && reqs[i].seq_len >= 1, "generate_batch: every request needs input_ids");
+        sample_len[i] = std::max<size_t>(reqs[i].params.max_tokens, 1);
+        AHA_REQUIRE(cap >= sample_len[i], "out_tokens capacity (per request) is smaller than max_tokens");
+        ents[i].slot = E.admit();
+        E.set_sampler(ents[i].slot, reqs[i].params);
+        ents[i].tokens = reqs[i].ids; ents[i].n = (int)reqs[i].seq_len; ents[i].sample = true;
+        n_out[i] = 0;
+        if (usage) { usage[i] = aha_usage{}; usage[i].prompt_tokens = (uint32_t)reqs[i].seq_len; }
+    }
+    std::vector<uint32_t> toks(n);
+    E.step(ents.data(), (int)n, nullptr, toks.data());
+    std::vector<size_t> act;
+    for (size_t i = 0; i < n; ++i) {
+        out_tokens[i * cap] = toks[i]; n_out[i] = 1;
+        const bool stop = (reqs[i].params.flags & AHA_GEN_EOS_ON_FIRST) != 0 && is_eos(toks[i]);
+        if (sample_len[i] > 1 && !stop) act.push_back(i); else E.release(ents[i].slot);
+    }
+    while (!act.empty()) {
+        std::vector<SeqStepEntry> st(act.size());
+        for (size_t k = 0; k < act.size(); ++k) { st[k].slot = ents[act[k]].slot; st[k].n = 1; st[k].sample = true; }
+        E.step(st.data(), (int)st.size(), nullptr, toks.data());
+        std::vector<size_t> next;
+        for (size_t k = 0; k < act.size(); ++k) {
+            const size_t i = act[k];
+            out_tokens[i * cap + n_out[i]] = toks[k]; n_out[i] += 1;
+            if (!(is_eos(toks[k]) || n_out[i] >= sample_len[i])) next.push_back(i); else E.release(ents[i].slot);
+        }
+        act.swap(next);
+    }
+    if (usage) for (size_t i = 0; i < n; ++i) usage[i].completion_tokens = (uint32_t)n_out[i];
+}
+
 // One request into slot `slot` of the batch decoder: the reference's forward_initial + sample_and_push on the slot's own page table (swapped into
 // the TextModel for the duration, so tower / M-RoPE / deepstack / sampler-on-prefill are the single-request code), then its decode state, history
 // and sampler move into the slot.  *swapped tells the caller's guard which table is swapped in if this throws.
@@ -909,13 +1091,13 @@ void generate_batch_impl(aha_model* m, const aha_batch_request* reqs, size_t n, 
 }
 }  // namespace
 
-int aha_b200_batch_open(aha_model* m) { return guarded(m, [&] { session_open(m); }); }
+int aha_b200_batch_open(aha_model* m) { return guarded(m, [&] { if (is_seq(m)) seq_session_open(m); else session_open(m); }); }
 
 int aha_b200_batch_add(aha_model* m, const aha_batch_request* req, int32_t* slot_out, uint32_t* first_token_out, int32_t* finished_out, aha_usage* usage) {
     return guarded(m, [&] {
         AHA_REQUIRE(req && slot_out && first_token_out && finished_out, "req, slot_out, first_token_out and finished_out are required");
         int slot = -1, fin = 0;
-        session_add(m, *req, &slot, first_token_out, &fin, usage);
+        if (is_seq(m)) seq_session_add(m, *req, &slot, first_token_out, &fin, usage); else session_add(m, *req, &slot, first_token_out, &fin, usage);
         *slot_out = slot; *finished_out = fin;
     });
 }
@@ -923,19 +1105,19 @@ int aha_b200_batch_add(aha_model* m, const aha_batch_request* req, int32_t* slot
 int aha_b200_batch_step(aha_model* m, uint32_t* tokens_out, int32_t* status_out, size_t* n_stepped_out) {
     return guarded(m, [&] {
         AHA_REQUIRE(tokens_out && status_out, "tokens_out[8] and status_out[8] are required");
-        const size_t n = session_step(m, tokens_out, status_out);
+        const size_t n = is_seq(m) ? seq_session_step(m, tokens_out, status_out) : session_step(m, tokens_out, status_out);
         if (n_stepped_out) *n_stepped_out = n;
     });
 }
 
 int aha_b200_batch_close(aha_model* m) {
-    return guarded(m, [&] { AHA_CUDA_CHECK(cudaStreamSynchronize(m->ctx.stream)); session_close(m); });
+    return guarded(m, [&] { AHA_CUDA_CHECK(cudaStreamSynchronize(m->ctx.stream)); if (is_seq(m)) seq_drop(m); else session_close(m); });
 }
 
 int aha_b200_generate_batch(aha_model* m, const aha_batch_request* reqs, size_t n, uint32_t* out_tokens, size_t cap, size_t* n_out, aha_usage* usage) {
     return guarded(m, [&] {
         AHA_REQUIRE(reqs && out_tokens && n_out, "reqs, out_tokens and n_out are required");
-        generate_batch_impl(m, reqs, n, out_tokens, cap, n_out, usage);
+        if (is_seq(m)) seq_generate_batch(m, reqs, n, out_tokens, cap, n_out, usage); else generate_batch_impl(m, reqs, n, out_tokens, cap, n_out, usage);
     });
 }
 
@@ -947,7 +1129,8 @@ int aha_b200_generate(aha_model* m, const uint32_t* ids, size_t seq_len, const a
         if (usage) *usage = aha_usage{};
         size_t n = 0;
         GenSink sink{[&](uint32_t t, size_t i) { out_tokens[i] = t; n = i + 1; return false; }};
-        generate_impl(m, ids, seq_len, mm, *params, sink, false, usage, nullptr);
+        if (is_seq(m)) seq_generate(m, ids, seq_len, *params, sink, usage);
+        else generate_impl(m, ids, seq_len, mm, *params, sink, false, usage, nullptr);
         *n_out = n;
     });
 }
@@ -958,13 +1141,15 @@ int aha_b200_generate_stream(aha_model* m, const uint32_t* ids, size_t seq_len, 
         AHA_REQUIRE(params && on_token, "params and on_token are required");
         if (usage) *usage = aha_usage{};
         GenSink sink{[&](uint32_t t, size_t i) { return on_token(user, t, (uint32_t)i) != 0; }};
-        generate_impl(m, ids, seq_len, mm, *params, sink, true, usage, nullptr);
+        if (is_seq(m)) seq_generate(m, ids, seq_len, *params, sink, usage);
+        else generate_impl(m, ids, seq_len, mm, *params, sink, true, usage, nullptr);
     });
 }
 
 int aha_b200_asr_generate(aha_model* m, const aha_asr_chunk* chunks, size_t n_chunks, const aha_gen_params* params, uint32_t* out_tokens, size_t cap,
                           size_t* n_out, aha_token_callback on_token, void* user, aha_usage* usage) {
     return guarded(m, [&] {
+        require_text(m, "aha_b200_asr_generate");
         AHA_REQUIRE(m->kind == aha_model::QWEN3_ASR, "asr_generate needs a qwen3_asr handle");
         AHA_REQUIRE(chunks && n_chunks >= 1 && params && out_tokens && n_out, "chunks, params, out_tokens and n_out are required");
         if (usage) *usage = aha_usage{};
@@ -997,6 +1182,7 @@ int aha_b200_asr_generate(aha_model* m, const aha_asr_chunk* chunks, size_t n_ch
 int aha_b200_debug_sample(aha_model* m, const float* logits, const aha_gen_params* params, const uint32_t* context, size_t n_context,
                           uint32_t draw_index, uint32_t* token_out) {
     return guarded(m, [&] {
+        require_text(m, "aha_b200_debug_sample");
         AHA_REQUIRE(logits && params && token_out && (context || n_context == 0), "logits, params and token_out are required");
         TextModel& T = m->text;
         AHA_REQUIRE(n_context <= (size_t)T.hist_cap, "context longer than the history buffer");
@@ -1017,6 +1203,7 @@ int aha_b200_debug_sample(aha_model* m, const float* logits, const aha_gen_param
 
 int aha_b200_decode_steps(aha_model* m, uint32_t first_token, size_t seqlen_offset, size_t n_steps, uint32_t* out_tokens, double* device_ms) {
     return guarded(m, [&] {
+        require_text(m, "aha_b200_decode_steps");
         TextModel& T = m->text;
         AHA_REQUIRE(first_token < (uint32_t)T.cfg.V, "token id out of range");
         AHA_REQUIRE(seqlen_offset + n_steps <= (size_t)T.max_ctx, "context exceeds max_ctx");
@@ -1040,6 +1227,7 @@ int aha_b200_decode_steps(aha_model* m, uint32_t first_token, size_t seqlen_offs
 
 int aha_b200_bench_kernel(aha_model* m, const char* which, int iters, double* avg_ms, uint64_t* bytes_per_launch) {
     return guarded(m, [&] {
+        require_text(m, "aha_b200_bench_kernel");
         AHA_REQUIRE(which && iters > 0 && avg_ms && bytes_per_launch, "which, iters, avg_ms, bytes_per_launch are required");
         TextModel& T = m->text;
         const std::string w = which;
@@ -1381,6 +1569,7 @@ int aha_b200_split_audio_into_chunks(size_t total_len, uint32_t sample_rate, flo
 int aha_b200_debug_gemm(aha_model* m, int impl, int epi, int act, int M, int N, int K, const float* x, const uint16_t* w, const float* bias,
                         const float* resid, float* out, int iters, double* device_ms) {
     return guarded(m, [&] {
+        require_text(m, "aha_b200_debug_gemm");
         AHA_REQUIRE(x && w && out && M > 0 && N > 0 && K > 0, "x, w, out and positive sizes are required");
         Ctx& c = m->ctx;
         float *dx = nullptr, *db = nullptr, *dr = nullptr, *dy = nullptr;
@@ -1463,12 +1652,14 @@ void embed_one(aha_model* m, const uint32_t* ids, size_t S, float* out) {
 }  // namespace
 
 int aha_b200_embed(aha_model* m, const uint32_t* ids, size_t seq_len, float* out) {
-    return guarded(m, [&] { embed_one(m, ids, seq_len, out); });
+    return guarded(m, [&] {
+        require_text(m, "aha_b200_embed"); embed_one(m, ids, seq_len, out); });
 }
 
 int aha_b200_rerank(aha_model* m, const uint32_t* query_ids, size_t query_len, const uint32_t* doc_ids, const size_t* doc_lens, size_t n_docs,
                     float* scores_out) {
     return guarded(m, [&] {
+        require_text(m, "aha_b200_rerank");
         AHA_REQUIRE(doc_ids && doc_lens && scores_out && n_docs >= 1, "documents are required (embedding input cannot be empty)");
         const int H = m->text.cfg.H;
         std::vector<float> q(H), d(H);
@@ -1529,10 +1720,55 @@ int aha_b200_rope_index(const uint32_t* ids, size_t seq_len, const uint32_t* gri
                                   rope_delta_out);
 }
 
+/* ---- explicit sequence control on a layered-engine handle (see the header) ---- */
+int aha_b200_seq_open(aha_model* m, int32_t* slot_out) {
+    return guarded(m, [&] {
+        AHA_REQUIRE(is_seq(m), "sequence entries need a layered-engine handle");
+        AHA_REQUIRE(slot_out, "slot_out is required");
+        require_no_session(m);
+        *slot_out = m->seq->admit();
+    });
+}
+int aha_b200_seq_close(aha_model* m, int32_t slot) {
+    return guarded(m, [&] {
+        AHA_REQUIRE(is_seq(m), "sequence entries need a layered-engine handle");
+        AHA_CUDA_CHECK(cudaStreamSynchronize(m->ctx.stream));
+        m->seq->release(slot);
+        if (m->seq_single == slot) m->seq_single = -1;
+    });
+}
+int aha_b200_seq_feed(aha_model* m, const aha_feed_entry* entries, size_t n, float* logits_out, size_t cap_rows) {
+    return guarded(m, [&] {
+        AHA_REQUIRE(is_seq(m), "sequence entries need a layered-engine handle");
+        AHA_REQUIRE(entries && n >= 1, "entries are required");
+        require_no_session(m);
+        std::vector<SeqStepEntry> ents(n);
+        size_t rows = 0;
+        for (size_t i = 0; i < n; ++i) {
+            ents[i].slot = entries[i].slot; ents[i].tokens = entries[i].ids; ents[i].n = (int)entries[i].n;
+            ents[i].want = entries[i].want; ents[i].n_want = (int)entries[i].n_want;
+            AHA_REQUIRE(entries[i].ids, "feed: every entry needs token ids");
+            rows += entries[i].n_want;
+        }
+        AHA_REQUIRE(rows == 0 || (logits_out && cap_rows >= rows), "logits_out is too small for the wanted rows");
+        m->seq->step(ents.data(), (int)n, rows ? logits_out : nullptr, nullptr);
+        AHA_CUDA_CHECK(cudaStreamSynchronize(m->ctx.stream));
+    });
+}
+int aha_b200_seq_info(aha_model* m, int32_t slot, int64_t* position_out, int64_t* free_tokens_out, int32_t* max_seqs_out) {
+    return guarded(m, [&] {
+        AHA_REQUIRE(is_seq(m), "sequence entries need a layered-engine handle");
+        if (position_out) *position_out = slot >= 0 ? m->seq->position(slot) : 0;
+        if (free_tokens_out) *free_tokens_out = (int64_t)m->seq->free_tokens();
+        if (max_seqs_out) *max_seqs_out = m->seq->max_seqs();
+    });
+}
+
 void aha_b200_destroy(aha_model* m) {
     if (!m) return;
     cudaSetDevice(m->ctx.device);
     if (m->ctx.stream) cudaStreamSynchronize(m->ctx.stream);
+    m->seq.reset();
     m->text.destroy();
     m->batch.clear_graphs();
     m->ctx.free_all();
@@ -1559,6 +1795,13 @@ int aha_b200_get_stats(aha_model* m, aha_stats* out) {
         AHA_REQUIRE(out, "out is required");
         out->kernel_launches = m->ctx.cnt.kernels;
         out->graph_launches = m->ctx.cnt.graphs;
+        if (is_seq(m)) {
+            out->kernels_per_decode_step = 0;
+            out->weight_bytes = m->seq->weight_bytes();
+            out->kv_bytes_per_token = m->seq->kv_bytes_per_token();
+            out->decode_bytes_per_step_fixed = m->seq->weight_bytes();
+            return;
+        }
         out->kernels_per_decode_step = m->text.step_graph_kernels;
         out->weight_bytes = m->ctx.alloc_bytes;
         out->kv_bytes_per_token = (uint64_t)m->text.cfg.L * 2 * m->text.nkv_l * m->text.cfg.hd * sizeof(float);
@@ -1570,6 +1813,7 @@ int aha_b200_reset_stats(aha_model* m) {
 }
 int aha_b200_set_trace(aha_model* m, int on) {
     return guarded(m, [&] {
+        if (is_seq(m)) { m->seq->set_trace(on != 0); return; }
         m->text.set_trace(on != 0);
         if (m->kind == aha_model::QWEN3VL) m->vision.set_trace(on != 0);
         if (m->kind == aha_model::QWEN3_ASR) m->audio.set_trace(on != 0);
@@ -1579,6 +1823,11 @@ int aha_b200_debug_read(aha_model* m, const char* what, int index, float* out, s
     return guarded(m, [&] {
         AHA_REQUIRE(what && out && n, "what, out and n are required");
         const std::string w = what;
+        if (is_seq(m)) {   // "hidden": the residual stream after layer `index` for the tokens of the last launch
+            AHA_REQUIRE(w == "hidden", "a layered-engine handle traces \"hidden\" only");
+            *n = m->seq->read_trace(index, out, cap);
+            return;
+        }
         const float* src = nullptr;
         size_t cnt = 0;
         TextModel& T = m->text;

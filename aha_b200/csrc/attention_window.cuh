@@ -1,0 +1,208 @@
+// attention_window.cuh -- the ragged attention path: sequences of unequal length in one launch, keys / values in the paged cache.
+//
+//   qkv_conv_norm_kernel   what happens between the q/k/v projection and the cache: an optional short causal convolution per channel
+//                          (y_t = sum_j w[c][j] u_{t - taps + 1 + j}; the taps - 1 projected values before a step are the sequence's conv
+//                          state), an optional RMS norm of q and of k over the WHOLE projection (all heads at once), then K (convolved,
+//                          normed) and V (convolved) go to the cache at the token's position and q to a dense buffer
+//   conv_tail_update_kernel  leaves the last taps - 1 projected values of every entry in its slot
+//   window_attn_kernel     softmax attention of query head h over kv head h / (H / G) with
+//                              score(i, j) = q_i . k_j * scale - slope_h * (i - j),   visible: 0 <= i - j < window  (window 0: all j <= i)
+//                          and an optional sigmoid output gate.  slope_h comes from a table, so any bias schedule can be passed.
+// Positions, scores, softmax weights and norms are fp32; the cache is fp32.  A token's result depends only on its own sequence.
+#pragma once
+#include "common.cuh"
+#include "ragged.cuh"
+
+namespace aha {
+
+constexpr int kConvMaxTaps = 16;
+
+struct PagedKV {           // one layer's cache: K pages [page][G][kPage][D], V pages [page][G][kPage][Dv]
+    float* k = nullptr;
+    float* v = nullptr;
+    int G = 0, D = 0, Dv = 0;
+    __device__ __forceinline__ float* k_row(int page, int g, int tok_in_page) const { return k + (((size_t)page * G + g) * kPage + tok_in_page) * D; }
+    __device__ __forceinline__ float* v_row(int page, int g, int tok_in_page) const { return v + (((size_t)page * G + g) * kPage + tok_in_page) * Dv; }
+};
+
+struct QkvPrepArgs {
+    const float* proj; int ld;       // [T, ld] projected rows (bias added)
+    int q_off, k_off, v_off;         // column of the first q / k / v channel in a row
+    int Cq, Ck, Cv;                  // channels (Ck = Cv = 0: the layer reads another layer's cache)
+    int taps;                        // 0 / 1: no convolution
+    const float *wq, *wk, *wv;       // [C, taps]
+    float* tails;                    // [slots][taps - 1][Cq + Ck + Cv]
+    size_t tail_slot_stride;
+    const float *q_norm, *k_norm;    // [Cq], [Ck] or nullptr
+    float eps;
+    float* q_out;                    // [T, Cq]
+    PagedKV kv;
+    RaggedBatch rb;
+};
+
+// projected value of channel (off + c) `back` tokens before packed token t, taken from this step's rows or from the slot's tail
+__device__ __forceinline__ float conv_input(const QkvPrepArgs& a, int t, int local, int pos, const float* tail, int ctot, int coff, int off, int c, int back) {
+    if (local - back >= 0) return a.proj[(size_t)(t - back) * a.ld + off + c];
+    if (pos - back < 0) return 0.f;                                  // before the sequence's start
+    return tail[(size_t)(a.taps - 1 + local - back) * ctot + coff + c];
+}
+
+static __global__ void __launch_bounds__(256) qkv_conv_norm_kernel(QkvPrepArgs a) {
+    __shared__ float red[32];
+    const int t = blockIdx.x;
+    const int e = a.rb.tok_entry[t], pos = a.rb.tok_pos[t], local = t - a.rb.ent_start[e], slot = a.rb.ent_slot[e];
+    const int ctot = a.Cq + a.Ck + a.Cv;
+    const float* tail = a.tails ? a.tails + (size_t)slot * a.tail_slot_stride : nullptr;
+    const bool conv = a.taps > 1;
+    auto value = [&](const float* w, int coff, int off, int c) {
+        if (!conv) return a.proj[(size_t)t * a.ld + off + c];
+        float y = 0.f;
+        for (int j = 0; j < a.taps; ++j) y = fmaf(w[(size_t)c * a.taps + j], conv_input(a, t, local, pos, tail, ctot, coff, off, c, a.taps - 1 - j), y);
+        return y;
+    };
+    // q
+    {
+        float ss = 0.f;
+        float* qo = a.q_out + (size_t)t * a.Cq;
+        for (int c = threadIdx.x; c < a.Cq; c += blockDim.x) { const float y = value(a.wq, 0, a.q_off, c); qo[c] = y; ss = fmaf(y, y, ss); }
+        if (a.q_norm) {
+            ss = block_sum(ss, red);
+            const float inv = 1.0f / sqrtf(ss / (float)a.Cq + a.eps);
+            for (int c = threadIdx.x; c < a.Cq; c += blockDim.x) qo[c] = qo[c] * inv * a.q_norm[c];
+        }
+    }
+    if (a.Ck == 0) return;
+    const int page = a.rb.page_tables[(size_t)slot * a.rb.max_pages + (pos >> kPageShift)], tip = pos & (kPage - 1);
+    {
+        float ss = 0.f;
+        for (int c = threadIdx.x; c < a.Ck; c += blockDim.x) {
+            const float y = value(a.wk, a.Cq, a.k_off, c);
+            a.kv.k_row(page, c / a.kv.D, tip)[c % a.kv.D] = y;
+            ss = fmaf(y, y, ss);
+        }
+        if (a.k_norm) {
+            ss = block_sum(ss, red);
+            const float inv = 1.0f / sqrtf(ss / (float)a.Ck + a.eps);
+            for (int c = threadIdx.x; c < a.Ck; c += blockDim.x) { float* p = a.kv.k_row(page, c / a.kv.D, tip) + c % a.kv.D; *p = *p * inv * a.k_norm[c]; }
+        }
+    }
+    for (int c = threadIdx.x; c < a.Cv; c += blockDim.x) a.kv.v_row(page, c / a.kv.Dv, tip)[c % a.kv.Dv] = value(a.wv, a.Cq + a.Ck, a.v_off, c);
+}
+
+// One block per entry: new tail[r] = projected value at local index n - (taps - 1) + r, from this step's rows where that index is >= 0, else
+// from the old tail (shifted by n), else zero (before the sequence's start).  A thread reads all it needs of its channel before it writes.
+static __global__ void __launch_bounds__(256) conv_tail_update_kernel(QkvPrepArgs a) {
+    const int e = blockIdx.x;
+    const int t0 = a.rb.ent_start[e], n = a.rb.ent_start[e + 1] - t0, pos0 = a.rb.ent_pos0[e], slot = a.rb.ent_slot[e];
+    const int ctot = a.Cq + a.Ck + a.Cv, nt = a.taps - 1;
+    float* tail = a.tails + (size_t)slot * a.tail_slot_stride;
+    for (int c = threadIdx.x; c < ctot; c += blockDim.x) {
+        const int off = c < a.Cq ? a.q_off + c : (c < a.Cq + a.Ck ? a.k_off + c - a.Cq : a.v_off + c - a.Cq - a.Ck);
+        float v[kConvMaxTaps];
+#pragma unroll
+        for (int r = 0; r < kConvMaxTaps; ++r) {
+            if (r >= nt) break;
+            const int li = n - nt + r;
+            v[r] = li >= 0 ? a.proj[(size_t)(t0 + li) * a.ld + off] : (pos0 + li < 0 ? 0.f : tail[(size_t)(r + n) * ctot + c]);
+        }
+#pragma unroll
+        for (int r = 0; r < kConvMaxTaps; ++r) {
+            if (r >= nt) break;
+            tail[(size_t)r * ctot + c] = v[r];
+        }
+    }
+}
+
+struct WindowAttnArgs {
+    const float* q;          // [T, H*D]
+    PagedKV kv;
+    const float* slopes;     // [H] distance penalty per head (0 = none)
+    float scale;
+    int window;              // 0 = every earlier position
+    const float* gate; int gate_ld;   // raw gate pre-activations [T, .] (column h*Dv + c) or nullptr
+    float* out;              // [T, H*Dv]
+    int H;
+    RaggedBatch rb;
+};
+
+constexpr int kWinAttnThreads = 128;
+constexpr int kWinAttnMaxAcc = 4;    // Dv <= 4 * 128
+
+static __global__ void __launch_bounds__(kWinAttnThreads) window_attn_kernel(WindowAttnArgs a) {
+    extern __shared__ float sm[];
+    const int D = a.kv.D, Dv = a.kv.Dv;
+    float* qs = sm;                 // [D]
+    float* sc = sm + D;             // [threads]
+    float* red = sc + kWinAttnThreads;   // [32]
+    const int t = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
+    const int g = h / (a.H / a.kv.G);
+    const int e = a.rb.tok_entry[t], i = a.rb.tok_pos[t], slot = a.rb.ent_slot[e];
+    const int* pt = a.rb.page_tables + (size_t)slot * a.rb.max_pages;
+    const float slope = a.slopes ? a.slopes[h] : 0.f;
+    for (int d = tid; d < D; d += kWinAttnThreads) qs[d] = a.q[(size_t)t * a.H * D + h * D + d];
+    __syncthreads();
+    const int j0 = a.window > 0 ? max(0, i - a.window + 1) : 0;
+    float m = -INFINITY, l = 0.f;
+    float acc[kWinAttnMaxAcc];
+#pragma unroll
+    for (int r = 0; r < kWinAttnMaxAcc; ++r) acc[r] = 0.f;
+    for (int jb = j0; jb <= i; jb += kWinAttnThreads) {
+        const int j = jb + tid;
+        float s = -INFINITY;
+        if (j <= i) {
+            const float* kr = a.kv.k_row(pt[j >> kPageShift], g, j & (kPage - 1));
+            float dot = 0.f;
+            for (int d = 0; d < D; ++d) dot = fmaf(qs[d], kr[d], dot);
+            s = dot * a.scale - slope * (float)(i - j);
+        }
+        const float m_new = fmaxf(m, block_max(s, red));
+        const float p = j <= i ? expf(s - m_new) : 0.f;
+        const float corr = expf(m - m_new);          // m = -inf on the first tile: 0
+        sc[tid] = p;
+        const float psum = block_sum(p, red);          // its barriers publish sc
+        l = l * corr + psum;
+        m = m_new;
+        const int nj = min(kWinAttnThreads, i - jb + 1);
+#pragma unroll
+        for (int r = 0; r < kWinAttnMaxAcc; ++r) {
+            const int c = tid + r * kWinAttnThreads;
+            if (c < Dv) {
+                float o = acc[r] * corr;
+                for (int jj = 0; jj < nj; ++jj) {
+                    const int jk = jb + jj;
+                    o = fmaf(sc[jj], a.kv.v_row(pt[jk >> kPageShift], g, jk & (kPage - 1))[c], o);
+                }
+                acc[r] = o;
+            }
+        }
+        __syncthreads();     // sc is rewritten by the next tile
+    }
+    const float inv = 1.0f / l;
+#pragma unroll
+    for (int r = 0; r < kWinAttnMaxAcc; ++r) {
+        const int c = tid + r * kWinAttnThreads;
+        if (c < Dv) {
+            float o = acc[r] * inv;
+            if (a.gate) o *= sigmoid_f(a.gate[(size_t)t * a.gate_ld + h * Dv + c]);
+            a.out[(size_t)t * a.H * Dv + h * Dv + c] = o;
+        }
+    }
+}
+
+inline void qkv_prepare(cudaStream_t st, const QkvPrepArgs& a) {
+    if (a.rb.T == 0) return;
+    AHA_REQUIRE(a.taps <= kConvMaxTaps, "short convolution: more than 16 taps");
+    qkv_conv_norm_kernel<<<a.rb.T, 256, 0, st>>>(a);
+    if (a.taps > 1) conv_tail_update_kernel<<<a.rb.E, 256, 0, st>>>(a);
+    AHA_CUDA_CHECK(cudaGetLastError());
+}
+
+inline void window_attn(cudaStream_t st, const WindowAttnArgs& a) {
+    if (a.rb.T == 0) return;
+    AHA_REQUIRE(a.kv.Dv <= kWinAttnMaxAcc * kWinAttnThreads, "window attention: value head size above 512");
+    const size_t smem = ((size_t)a.kv.D + kWinAttnThreads + 32) * sizeof(float);
+    window_attn_kernel<<<dim3(a.rb.T, a.H), kWinAttnThreads, smem, st>>>(a);
+    AHA_CUDA_CHECK(cudaGetLastError());
+}
+
+}  // namespace aha

@@ -90,6 +90,13 @@ __device__ __forceinline__ float gelu_tanh_f(float x) {
     return 0.5f * x * (1.f + tanhf(c * (x + 0.044715f * x * x * x)));
 }
 
+// xIELU with its two parameters already mapped to their positive ranges (alpha_p = softplus(p), alpha_n = 1/2 + softplus(q)):
+// z > 0: alpha_p z^2 + z/2;  z <= 0: alpha_n (exp(z) - 1 - z) + z/2.
+__device__ __forceinline__ float xielu_f(float z, float alpha_p, float alpha_n) {
+    return z > 0.f ? fmaf(alpha_p * z, z, 0.5f * z) : fmaf(alpha_n, expm1f(z) - z, 0.5f * z);
+}
+__device__ __forceinline__ float sigmoid_f(float x) { return 1.f / (1.f + expf(-x)); }
+
 enum Act { ACT_NONE = 0, ACT_SILU = 1, ACT_GELU_ERF = 2, ACT_GELU_TANH = 3 };
 __device__ __forceinline__ float apply_act(int act, float x) {
     switch (act) {

@@ -1,0 +1,136 @@
+// gemm_any.cuh -- C[M,N] = epilogue(A[M,K] (fp32) x W[N,K]^T + bias) on the CUDA cores for ANY M, N, K and for weights stored as
+// fp32 or bf16.  Every product and every sum is fp32 (a bf16 weight widens exactly), so with fp32 weights this is the "true
+// 32-bit" path of a model, and with bf16 weights it is the exact twin of the tensor-core path.  Two kernels:
+//   gemm_any_kernel     64 x 64 tiles, bounds-checked on every side (sizes come from a checkpoint's config, nothing is assumed)
+//   gemm_skinny_kernel  M <= 8 rows (decode steps): one warp per output column streams that weight row once for all rows
+// Both accumulate a given output element in an order that depends only on (K, kernel), never on M or on the other rows.
+#pragma once
+#include <cuda_bf16.h>
+
+#include "common.cuh"
+
+namespace aha {
+
+enum AnyEpi { AEPI_STORE = 0, AEPI_XIELU = 1 };
+
+struct GemmAnyArgs {
+    const float* A; int lda;
+    const void* W;            // [N, K] row-major, float or __nv_bfloat16
+    const float* bias;        // [N] or nullptr
+    float* C; int ldc;
+    int M, N, K;
+    float act_a, act_b;       // AEPI_XIELU: alpha_p, alpha_n
+};
+
+__device__ __forceinline__ float wt_to_f(float v) { return v; }
+__device__ __forceinline__ float wt_to_f(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <int EPI>
+__device__ __forceinline__ float any_epilogue(const GemmAnyArgs& g, float v, int n) {
+    if (g.bias) v += g.bias[n];
+    if (EPI == AEPI_XIELU) v = xielu_f(v, g.act_a, g.act_b);
+    return v;
+}
+
+template <typename WT, int EPI>
+static __global__ void __launch_bounds__(256) gemm_any_kernel(GemmAnyArgs g) {
+    constexpr int BM = 64, BN = 64, BK = 16, PAD = 4;
+    __shared__ __align__(16) float As[BK][BM + PAD];
+    __shared__ __align__(16) float Bs[BK][BN + PAD];
+    const WT* __restrict__ W = reinterpret_cast<const WT*>(g.W);
+    const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+    const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+    const int lr = tid >> 2, lk = (tid & 3) * 4;
+    float acc[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+    const int m = m0 + lr, n = n0 + lr;
+    for (int k0 = 0; k0 < g.K; k0 += BK) {
+        float a[4], b[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int kk = k0 + lk + i;
+            a[i] = (m < g.M && kk < g.K) ? g.A[(size_t)m * g.lda + kk] : 0.f;
+            b[i] = (n < g.N && kk < g.K) ? wt_to_f(W[(size_t)n * g.K + kk]) : 0.f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int i = 0; i < 4; ++i) { As[lk + i][lr] = a[i]; Bs[lk + i][lr] = b[i]; }
+        __syncthreads();
+#pragma unroll
+        for (int k = 0; k < BK; ++k) {
+            const float4 a4 = *reinterpret_cast<const float4*>(&As[k][ty * 4]);
+            const float4 b4 = *reinterpret_cast<const float4*>(&Bs[k][tx * 4]);
+            const float av[4] = {a4.x, a4.y, a4.z, a4.w}, bv[4] = {b4.x, b4.y, b4.z, b4.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(av[i], bv[j], acc[i][j]);
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int mm = m0 + ty * 4 + i;
+        if (mm >= g.M) continue;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int nn = n0 + tx * 4 + j;
+            if (nn < g.N) g.C[(size_t)mm * g.ldc + nn] = any_epilogue<EPI>(g, acc[i][j], nn);
+        }
+    }
+}
+
+// M <= MB rows.  Warp w of the grid owns output columns w, w + warps, ...; lane l multiplies elements l, l + 32, ... of the weight row with
+// the same elements of every activation row (L1-resident), then the warp tree-sums.  The weight matrix is read exactly once per launch.
+template <typename WT, int EPI, int MB>
+static __global__ void __launch_bounds__(256) gemm_skinny_kernel(GemmAnyArgs g) {
+    const WT* __restrict__ W = reinterpret_cast<const WT*>(g.W);
+    const int lane = threadIdx.x & 31;
+    const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, nwarps = (gridDim.x * blockDim.x) >> 5;
+    for (int n = warp; n < g.N; n += nwarps) {
+        const WT* wr = W + (size_t)n * g.K;
+        float acc[MB];
+#pragma unroll
+        for (int r = 0; r < MB; ++r) acc[r] = 0.f;
+        for (int k = lane; k < g.K; k += 32) {
+            const float w = wt_to_f(wr[k]);
+#pragma unroll
+            for (int r = 0; r < MB; ++r)
+                if (r < g.M) acc[r] = fmaf(g.A[(size_t)r * g.lda + k], w, acc[r]);
+        }
+#pragma unroll
+        for (int r = 0; r < MB; ++r) {
+            const float v = warp_sum(acc[r]);
+            if (lane == 0 && r < g.M) g.C[(size_t)r * g.ldc + n] = any_epilogue<EPI>(g, v, n);
+        }
+    }
+}
+
+template <typename WT, int EPI>
+inline void gemm_any_launch(cudaStream_t st, const GemmAnyArgs& g, int num_sms) {
+    if (g.M <= 8) {
+        const int blocks = std::max(1, std::min(ceil_div(g.N, 8), num_sms * 8));
+        if (g.M <= 1) gemm_skinny_kernel<WT, EPI, 1><<<blocks, 256, 0, st>>>(g);
+        else if (g.M <= 2) gemm_skinny_kernel<WT, EPI, 2><<<blocks, 256, 0, st>>>(g);
+        else if (g.M <= 4) gemm_skinny_kernel<WT, EPI, 4><<<blocks, 256, 0, st>>>(g);
+        else gemm_skinny_kernel<WT, EPI, 8><<<blocks, 256, 0, st>>>(g);
+    } else {
+        gemm_any_kernel<WT, EPI><<<dim3(ceil_div(g.N, 64), ceil_div(g.M, 64)), 256, 0, st>>>(g);
+    }
+}
+
+// fp32_weights: W holds floats, else bf16
+inline void gemm_any(cudaStream_t st, int epi, bool fp32_weights, const GemmAnyArgs& g, int num_sms) {
+    if (g.M == 0 || g.N == 0) return;
+    AHA_REQUIRE(epi == AEPI_STORE || epi == AEPI_XIELU, "gemm_any: bad epilogue");
+    if (fp32_weights) {
+        if (epi == AEPI_STORE) gemm_any_launch<float, AEPI_STORE>(st, g, num_sms); else gemm_any_launch<float, AEPI_XIELU>(st, g, num_sms);
+    } else {
+        if (epi == AEPI_STORE) gemm_any_launch<__nv_bfloat16, AEPI_STORE>(st, g, num_sms); else gemm_any_launch<__nv_bfloat16, AEPI_XIELU>(st, g, num_sms);
+    }
+    AHA_CUDA_CHECK(cudaGetLastError());
+}
+
+}  // namespace aha

@@ -2,12 +2,14 @@
 // All activations are fp32; linear weights are fp16 (lossless for the fp16 checkpoints) and every
 // product is formed in fp32 -- the same arithmetic as the reference's Candle F32 CPU path.
 #pragma once
+#include <cuda_bf16.h>
+
 #include "common.cuh"
 
 namespace aha {
 
 // Embedding::forward (row gather), fp16 table -> fp32 rows.  /root/reference/src/models/qwen3/model.rs:191-193
-__global__ void embed_gather_kernel(const uint32_t* __restrict__ ids, const __half* __restrict__ table,
+static __global__ void embed_gather_kernel(const uint32_t* __restrict__ ids, const __half* __restrict__ table,
                                     float* __restrict__ out, int S, int H, int V) {
     const int s = blockIdx.x;
     uint32_t id = ids[s];
@@ -20,7 +22,7 @@ __global__ void embed_gather_kernel(const uint32_t* __restrict__ ids, const __ha
 }
 
 // candle_nn RmsNorm over the last dim: x / sqrt(mean(x^2) + eps) * w.  One block per row.
-__global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ w, float eps,
+static __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ w, float eps,
                                float* __restrict__ out, int H) {
     __shared__ float red[32];
     const float* xr = x + (size_t)blockIdx.x * H;
@@ -38,7 +40,7 @@ __device__ __forceinline__ void split_half(float x, __half& h, __half& l) {
     l = __float2half_rn(x - __half2float(h));
 }
 // rmsnorm_kernel with the split output: out_hi / out_lo [rows, H] fp16
-__global__ void rmsnorm_split_kernel(const float* __restrict__ x, const float* __restrict__ w, float eps, __half* __restrict__ out_hi,
+static __global__ void rmsnorm_split_kernel(const float* __restrict__ x, const float* __restrict__ w, float eps, __half* __restrict__ out_hi,
                                      __half* __restrict__ out_lo, int H) {
     __shared__ float red[32];
     const float* xr = x + (size_t)blockIdx.x * H;
@@ -54,7 +56,7 @@ __global__ void rmsnorm_split_kernel(const float* __restrict__ x, const float* _
     }
 }
 // layernorm_kernel with the split output
-__global__ void layernorm_split_kernel(const float* __restrict__ x, const float* __restrict__ w, const float* __restrict__ b, float eps,
+static __global__ void layernorm_split_kernel(const float* __restrict__ x, const float* __restrict__ w, const float* __restrict__ b, float eps,
                                        __half* __restrict__ out_hi, __half* __restrict__ out_lo, int H) {
     __shared__ float red[32];
     const float* xr = x + (size_t)blockIdx.x * H;
@@ -73,7 +75,7 @@ __global__ void layernorm_split_kernel(const float* __restrict__ x, const float*
 }
 
 // candle_nn LayerNorm (remove_mean, affine): (x-mean)/sqrt(var+eps)*w+b.  One block per row of length H.
-__global__ void layernorm_kernel(const float* __restrict__ x, const float* __restrict__ w,
+static __global__ void layernorm_kernel(const float* __restrict__ x, const float* __restrict__ w,
                                  const float* __restrict__ b, float eps, float* __restrict__ out, int H) {
     __shared__ float red[32];
     const float* xr = x + (size_t)blockIdx.x * H;
@@ -89,7 +91,7 @@ __global__ void layernorm_kernel(const float* __restrict__ x, const float* __res
 
 // out[idx[r], :] = src[r, :]   (masked_scatter_dim0, /root/reference/src/utils/tensor_utils.rs:294-321)
 // add != 0: out[idx[r], :] += src[r, :]   (mask_index_add, tensor_utils.rs:466-470)
-__global__ void scatter_rows_kernel(const int* __restrict__ idx, const float* __restrict__ src,
+static __global__ void scatter_rows_kernel(const int* __restrict__ idx, const float* __restrict__ src,
                                     float* __restrict__ out, int H, int add) {
     const int r = blockIdx.x;
     float* o = out + (size_t)idx[r] * H;
@@ -98,7 +100,7 @@ __global__ void scatter_rows_kernel(const int* __restrict__ idx, const float* __
 }
 
 // l2_normalize (/root/reference/src/models/common/modules.rs:1287-1294): x / sqrt(sum(x^2) + 1e-6), one row per block.
-__global__ void l2_normalize_kernel(const float* __restrict__ x, float* __restrict__ out, int H) {
+static __global__ void l2_normalize_kernel(const float* __restrict__ x, float* __restrict__ out, int H) {
     __shared__ float red[32];
     const float* xr = x + (size_t)blockIdx.x * H;
     float ss = 0.f;
@@ -108,14 +110,14 @@ __global__ void l2_normalize_kernel(const float* __restrict__ x, float* __restri
     for (int i = threadIdx.x; i < H; i += blockDim.x) out[(size_t)blockIdx.x * H + i] = xr[i] * inv;
 }
 
-__global__ void add_inplace_kernel(float* __restrict__ x, const float* __restrict__ y, size_t n) {
+static __global__ void add_inplace_kernel(float* __restrict__ x, const float* __restrict__ y, size_t n) {
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) x[i] += y[i];
 }
 
 // Two-stage argmax, "first maximal index" like candle's Sampling::ArgMax.
 // Stage 1 is fused into the lm_head GEMV epilogue where possible; this standalone version covers logits[V].
-__global__ void argmax_partial_kernel(const float* __restrict__ logits, int V, float* __restrict__ pmax,
+static __global__ void argmax_partial_kernel(const float* __restrict__ logits, int V, float* __restrict__ pmax,
                                       int* __restrict__ pidx) {
     __shared__ float smax[32];
     __shared__ int sidx[32];
@@ -156,7 +158,7 @@ struct DecodeState {
     uint32_t n_draws;    // random draws the request's sampler has consumed (index into its ChaCha12 stream)
     uint32_t pad_[3];
 };
-__global__ void argmax_final_kernel(const float* __restrict__ pmax, const int* __restrict__ pidx, int n,
+static __global__ void argmax_final_kernel(const float* __restrict__ pmax, const int* __restrict__ pidx, int n,
                                     uint32_t* __restrict__ argmax_out, DecodeState* __restrict__ st,
                                     uint32_t* __restrict__ history, int hist_cap, int advance) {
     float best = -INFINITY;
@@ -181,6 +183,49 @@ __global__ void argmax_final_kernel(const float* __restrict__ pmax, const int* _
             st->n_hist += 1;
         }
     }
+}
+
+
+// ---- kernels of the ragged (varlen) path -------------------------------------------------------------------------------------------
+// Row gather from an embedding table stored as fp32 or bf16 (both widen exactly to the fp32 residual stream).
+template <typename WT>
+static __global__ void embed_gather_any_kernel(const uint32_t* __restrict__ ids, const WT* __restrict__ table, float* __restrict__ out, int H, int V) {
+    const int s = blockIdx.x;
+    uint32_t id = ids[s];
+    if (id >= (uint32_t)V) id = V - 1;  // the host validates; keep the kernel memory-safe regardless
+    const WT* row = table + (size_t)id * H;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) out[(size_t)s * H + i] = (float)row[i];
+}
+
+// Post-norm residual step with a scalar gain: x[row] += g * y[row] / sqrt(mean(y[row]^2) + eps).  The gain is ONE number (read from
+// device memory); the norm sits on the sublayer's output, the residual sum stays fp32.  One block per row.
+static __global__ void scalar_rmsnorm_add_kernel(float* __restrict__ x, const float* __restrict__ y, const float* __restrict__ gain, float eps, int H) {
+    __shared__ float red[32];
+    const float* yr = y + (size_t)blockIdx.x * H;
+    float* xr = x + (size_t)blockIdx.x * H;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) { const float v = yr[i]; ss = fmaf(v, v, ss); }
+    ss = block_sum(ss, red);
+    const float sc = gain[0] / sqrtf(ss / (float)H + eps);
+    for (int i = threadIdx.x; i < H; i += blockDim.x) xr[i] = fmaf(yr[i], sc, xr[i]);
+}
+
+// out[r] = g * x[rows[r]] / sqrt(mean(x[rows[r]]^2) + eps): the final norm of the rows whose logits are wanted, gathered on the way.
+static __global__ void scalar_rmsnorm_rows_kernel(const float* __restrict__ x, const int* __restrict__ rows, const float* __restrict__ gain, float eps,
+                                                  float* __restrict__ out, int H) {
+    __shared__ float red[32];
+    const float* xr = x + (size_t)rows[blockIdx.x] * H;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) { const float v = xr[i]; ss = fmaf(v, v, ss); }
+    ss = block_sum(ss, red);
+    const float sc = gain[0] / sqrtf(ss / (float)H + eps);
+    for (int i = threadIdx.x; i < H; i += blockDim.x) out[(size_t)blockIdx.x * H + i] = xr[i] * sc;
+}
+
+// Tokens that never left the device: packed token t of a ragged step is the last sampled token of slot fb_slot[t] (>= 0), else the id the host sent.
+static __global__ void feedback_tokens_kernel(uint32_t* __restrict__ tokens, const int* __restrict__ fb_slot, const DecodeState* __restrict__ states, int T) {
+    const int t = blockIdx.x * blockDim.x + threadIdx.x;
+    if (t < T && fb_slot[t] >= 0) tokens[t] = states[fb_slot[t]].token;
 }
 
 }  // namespace aha

@@ -13,6 +13,7 @@
 #pragma once
 #include <cstdint>
 
+#include "../../include/aha_b200.h"
 #include "common.cuh"
 #include "kernels_common.cuh"
 
@@ -139,7 +140,7 @@ __device__ int blocked_pick_dev(SampleSmem& s, int V, F w, float draw01, int* er
     return r;
 }
 
-__global__ void __launch_bounds__(kSampleThreads) sample_kernel(SampleArgs a) {
+static __global__ void __launch_bounds__(kSampleThreads) sample_kernel(SampleArgs a) {
     __shared__ SampleSmem s;
     const int tid = threadIdx.x, V = a.V;
     float* p = a.work;
@@ -327,6 +328,27 @@ __global__ void __launch_bounds__(kSampleThreads) sample_kernel(SampleArgs a) {
             st->token = (uint32_t)token;
             if (n_hist >= 1 && n_hist - 1 < a.hist_cap) a.history[n_hist - 1] = (uint32_t)token;
         }
+    }
+}
+
+
+// ---- host helpers shared by every model that drives sample_kernel
+// get_logit_processor (/root/reference/src/models/common/sample.rs:7-38): which Sampling a request's parameters select
+inline int sampling_mode(const aha_gen_params& p) {
+    const bool has_t = !(p.temperature < 1e-7f);
+    const bool has_k = p.top_k > 0, has_p = p.top_p > 0.f;
+    if (!has_t) return SAMPLE_ARGMAX;
+    if (!has_k) return has_p ? SAMPLE_TOPP : SAMPLE_ALL;
+    return has_p ? SAMPLE_TOPK_TOPP : SAMPLE_TOPK;
+}
+// rand_core::SeedableRng::seed_from_u64: eight PCG32 outputs fill the 32-byte ChaCha seed
+inline void sampler_key_from_seed(uint64_t seed, uint32_t key[8]) {
+    uint64_t stt = seed;
+    for (int i = 0; i < 8; ++i) {
+        stt = stt * 6364136223846793005ull + 11634580027462260723ull;
+        const uint32_t xs = (uint32_t)(((stt >> 18) ^ stt) >> 27);
+        const uint32_t rot = (uint32_t)(stt >> 59);
+        key[i] = (xs >> rot) | (xs << ((32u - rot) & 31u));
     }
 }
 

@@ -1,0 +1,581 @@
+// seq_engine.cu -- the layered sequence engine (see seq_engine.h): a model is a list of layers read from config.json,
+//     x += norm1(mixer(x));   x += norm2(ff(x))   (post-norms with a scalar gain; a layer may have no feed-forward)
+// run by ONE ragged step function: the tokens of all entries of a step are packed into [T, width] fp32 rows, every Linear is one
+// GEMM over all rows, and the mixers' sequence kernels (recurrence.cuh, attention_window.cuh) take the RaggedBatch description.
+// Mixers and feed-forwards are looked up by name in a registry, each with its sizes and constants read from its config entry:
+//     "hgrn2"      gated linear recurrence, matrix state per head in the slot pool            (recurrence.cuh)
+//     "attention"  windowed softmax attention with a linear distance penalty, q/k/v bias, short convolution, whole-projection
+//                  q/k norm, sigmoid output gate, optional reuse of an earlier layer's cache     (attention_window.cuh)
+//     "dense"      W_down xIELU(W_up x)
+// Memory: one free list of 32-token pages serves every layer that owns keys / values (K pages [page][G][32][D], V pages
+// [page][G][32][Dv], fp32); a sequence additionally owns a state slot (recurrent states, convolution tails, sampler state).
+// Precision: the residual stream, norms, gates, recurrent state, scores and softmax are fp32 in both modes; the Linear layers
+// multiply bf16 weights (serving mode) or the same values widened to fp32 (exact mode) with fp32 accumulation.
+#include "seq_engine.h"
+
+#include <algorithm>
+#include <functional>
+#include <memory>
+
+#include "attention_window.cuh"
+#include "gemm_any.cuh"
+#include "json.hpp"
+#include "kernels_common.cuh"
+#include "recurrence.cuh"
+#include "runtime.cuh"
+#include "sampling.cuh"
+
+namespace aha {
+namespace {
+
+inline double softplus_d(double z) { return std::log1p(std::exp(-std::fabs(z))) + std::max(z, 0.0); }
+
+struct LinearAny {
+    void* w = nullptr;    // [N, K] bf16 or fp32
+    float* b = nullptr;   // [N] or nullptr
+    int N = 0, K = 0;
+};
+
+struct Engine;
+
+// What a sublayer sees of a step: the packed rows and the engine's scratch.
+struct StepView {
+    Engine* eng;
+    RaggedBatch rb;
+    const float* x;     // [T, width] sublayer input (the residual stream)
+    float* y;           // [T, width] sublayer output (before its norm)
+};
+
+struct Sublayer {
+    virtual ~Sublayer() {}
+    virtual void run(const StepView& v) = 0;
+    virtual int proj_cols() const = 0;     // widest intermediate row this sublayer needs in Engine::proj
+    virtual int inner_cols() const = 0;    // ... in Engine::inner
+    virtual int q_cols() const { return 0; }
+    virtual uint64_t kv_bytes_per_token() const { return 0; }
+};
+
+struct Engine final : SeqEngine {
+    Ctx& c;
+    SeqEngineOptions opt;
+    int W = 0, V = 0, L = 0;
+    float eps = 1e-6f;
+    bool fp32 = false;
+    // weights
+    void* embed = nullptr;
+    LinearAny head;
+    float* final_gain = nullptr;
+    struct LayerRec { std::unique_ptr<Sublayer> mixer, ff; float *gain1 = nullptr, *gain2 = nullptr; };
+    std::vector<LayerRec> layers;
+    std::vector<Sublayer*> mixer_of_layer;   // for kv_from lookups while building
+    uint64_t wbytes = 0;
+    // pools
+    int num_pages = 0, max_pages = 0, slots = 0;
+    std::vector<int> free_pages;
+    std::vector<std::vector<int>> h_tables;   // [slot][mapped pages]
+    int* d_tables = nullptr;
+    struct Seq { bool live = false; int pos = 0; bool samp_active = false; SampleArgs samp{}; };
+    std::vector<Seq> seqs;
+    // step scratch
+    int Tmax = 0, Rmax = 0;
+    float *x = nullptr, *y = nullptr, *proj = nullptr, *inner = nullptr, *qbuf = nullptr, *hn = nullptr, *logits = nullptr;
+    int* d_meta = nullptr; int* h_meta = nullptr; size_t meta_ints = 0;
+    cudaEvent_t ev_meta = nullptr; bool meta_pending = false;
+    // sampler state per slot
+    DecodeState* d_states = nullptr; uint32_t* d_hist = nullptr; int hist_cap = 0; uint32_t* d_tok = nullptr;
+    float *pmax = nullptr, *sample_work = nullptr; int* pidx = nullptr; int* d_sample_err = nullptr; int n_pcand = 64;
+    // trace
+    bool trace = false; float* trace_buf = nullptr; int trace_T = 0;
+
+    Engine(Ctx& ctx, const SeqEngineOptions& o) : c(ctx), opt(o) {}
+
+    // ---------------------------------------------------------------- weights
+    // rows of several [N_i, K] tensors stacked into one matrix in the engine's storage type; absent bias parts are zeros
+    LinearAny load_linear(const WeightTable& wt, const std::vector<std::string>& names, const std::vector<int>& rows, int K, const std::vector<std::string>& biases) {
+        LinearAny Lw;
+        Lw.K = K;
+        for (int r : rows) Lw.N += r;
+        const size_t n = (size_t)Lw.N * K;
+        bool any_bias = false;
+        for (auto& b : biases) any_bias = any_bias || (!b.empty() && wt.has(b));
+        if (fp32) {
+            std::vector<float> st(n);
+            size_t o = 0;
+            for (size_t i = 0; i < names.size(); ++i) {
+                wt.expect(names[i], {rows[i], K});
+                const aha_tensor_desc& d = wt.get(names[i]);
+                const size_t ne = (size_t)rows[i] * K;
+                if (d.dtype == AHA_BF16) { const uint16_t* s = reinterpret_cast<const uint16_t*>(d.data); for (size_t k = 0; k < ne; ++k) st[o + k] = bf16_bits_to_float(s[k]); }
+                else for (size_t k = 0; k < ne; ++k) st[o + k] = WeightTable::at(d, k);
+                o += ne;
+            }
+            Lw.w = upload(c, st);
+        } else {
+            std::vector<uint16_t> st(n);
+            size_t o = 0;
+            for (size_t i = 0; i < names.size(); ++i) {
+                wt.expect(names[i], {rows[i], K});
+                const aha_tensor_desc& d = wt.get(names[i]);
+                const size_t ne = (size_t)rows[i] * K;
+                if (d.dtype == AHA_BF16) std::memcpy(st.data() + o, d.data, ne * 2);
+                else for (size_t k = 0; k < ne; ++k) {   // round to nearest even
+                    float f = WeightTable::at(d, k); uint32_t u; std::memcpy(&u, &f, 4);
+                    st[o + k] = (uint16_t)((u + 0x7FFFu + ((u >> 16) & 1u)) >> 16);
+                }
+                o += ne;
+            }
+            Lw.w = upload(c, st);
+        }
+        if (any_bias) {
+            std::vector<float> b((size_t)Lw.N, 0.f);
+            size_t o = 0;
+            for (size_t i = 0; i < names.size(); ++i) {
+                if (i < biases.size() && !biases[i].empty() && wt.has(biases[i])) { auto v = wt.vec_f32(biases[i], rows[i]); std::copy(v.begin(), v.end(), b.begin() + o); }
+                o += rows[i];
+            }
+            Lw.b = upload(c, b);
+        }
+        return Lw;
+    }
+    void gemm(int epi, const float* A, int lda, const LinearAny& Wt, float* C, int ldc, int M, float a0 = 0.f, float a1 = 0.f) {
+        GemmAnyArgs g{};
+        g.A = A; g.lda = lda; g.W = Wt.w; g.bias = Wt.b; g.C = C; g.ldc = ldc; g.M = M; g.N = Wt.N; g.K = Wt.K; g.act_a = a0; g.act_b = a1;
+        gemm_any(c.stream, epi, fp32, g, c.num_sms);
+        c.cnt.kernels++;
+    }
+
+    // ---------------------------------------------------------------- SeqEngine
+    int vocab() const override { return V; }
+    int max_seqs() const override { return slots; }
+    int page_tokens() const override { return kPage; }
+    size_t free_tokens() const override { return free_pages.size() * (size_t)kPage; }
+    uint64_t weight_bytes() const override { return wbytes; }
+    uint64_t kv_bytes_per_token() const override { uint64_t b = 0; for (auto& l : layers) b += l.mixer->kv_bytes_per_token(); return b; }
+    bool live(int slot) const override { return slot >= 0 && slot < slots && seqs[slot].live; }
+    int position(int slot) const override { AHA_REQUIRE(live(slot), "sequence slot is not live"); return seqs[slot].pos; }
+    int admit() override {
+        for (int s = 0; s < slots; ++s)
+            if (!seqs[s].live) { seqs[s] = Seq{}; seqs[s].live = true; return s; }
+        throw std::runtime_error("aha_b200: all " + std::to_string(slots) + " sequence slots are live");
+    }
+    void release(int slot) override {
+        AHA_REQUIRE(live(slot), "sequence slot is not live");
+        for (int p : h_tables[slot]) free_pages.push_back(p);
+        h_tables[slot].clear();
+        seqs[slot] = Seq{};
+    }
+    void release_all() override { for (int s = 0; s < slots; ++s) if (seqs[s].live) release(s); }
+    void set_sampler(int slot, const aha_gen_params& p) override {
+        AHA_REQUIRE(live(slot), "sequence slot is not live");
+        Seq& q = seqs[slot];
+        const int mode = sampling_mode(p);
+        const bool pen = !(p.repeat_penalty == 1.0f || p.repeat_last_n == 0);
+        q.samp_active = mode != SAMPLE_ARGMAX || pen;
+        DecodeState st{};
+        AHA_CUDA_CHECK(cudaMemcpyAsync(d_states + slot, &st, sizeof(st), cudaMemcpyHostToDevice, c.stream));
+        AHA_CUDA_CHECK(cudaStreamSynchronize(c.stream));   // `st` is a stack temporary
+        if (!q.samp_active) return;
+        AHA_REQUIRE(V <= kSampleThreads * kSampleChunk, "vocabulary too large for the device sampler");
+        AHA_REQUIRE(!(mode == SAMPLE_TOPK || mode == SAMPLE_TOPK_TOPP) || p.top_k >= V || p.top_k <= kSampleMaxTopK, "top_k > 1024 is not supported by the device sampler");
+        SampleArgs a{};
+        a.work = sample_work; a.V = V; a.mode = mode;
+        a.inv_temp = mode == SAMPLE_ARGMAX ? 1.0f : (float)(1.0 / (double)p.temperature);
+        a.top_p = p.top_p; a.top_k = p.top_k; a.penalty = p.repeat_penalty; a.last_n = p.repeat_last_n;
+        sampler_key_from_seed(p.seed, a.key);
+        a.st = d_states + slot; a.history = d_hist + (size_t)slot * hist_cap; a.hist_cap = hist_cap; a.token_out = d_tok + slot; a.error = d_sample_err;
+        a.overwrite = 1;
+        q.samp = a;
+    }
+    void set_trace(bool on) override {
+        if (on && !trace_buf) trace_buf = c.alloc<float>((size_t)L * Tmax * W);
+        trace = on;
+    }
+    size_t read_trace(int layer, float* out, size_t cap) override {
+        AHA_REQUIRE(trace_buf && layer >= 0 && layer < L, "no trace recorded for this layer");
+        const size_t n = (size_t)trace_T * W;
+        AHA_REQUIRE(cap >= n, "trace buffer too small");
+        AHA_CUDA_CHECK(cudaStreamSynchronize(c.stream));
+        AHA_CUDA_CHECK(cudaMemcpy(out, trace_buf + (size_t)layer * Tmax * W, n * sizeof(float), cudaMemcpyDeviceToHost));
+        return n;
+    }
+
+    // ---------------------------------------------------------------- the step
+    struct Piece { int ent, off, cnt; };
+
+    void step(const SeqStepEntry* ents, int n, float* logits_out, uint32_t* tokens_out) override {
+        AHA_REQUIRE(n >= 1 && ents, "step: no entries");
+        std::vector<char> seen(slots, 0);
+        std::vector<size_t> row_base(n + 1, 0);
+        for (int i = 0; i < n; ++i) {
+            const SeqStepEntry& e = ents[i];
+            AHA_REQUIRE(live(e.slot), "step: entry names a slot that is not live");
+            AHA_REQUIRE(!seen[e.slot], "step: a sequence appears twice in one step");
+            seen[e.slot] = 1;
+            AHA_REQUIRE(e.n >= 1, "step: an entry brings no tokens");
+            AHA_REQUIRE(e.tokens || e.n == 1, "step: a fed-back token is a single token");
+            for (int k = 0; k < e.n_want; ++k) AHA_REQUIRE(e.want[k] >= 0 && e.want[k] < e.n && (k == 0 || e.want[k] > e.want[k - 1]), "step: `want` must be ascending indices into the entry's tokens");
+            if (e.tokens) for (int k = 0; k < e.n; ++k) AHA_REQUIRE(e.tokens[k] < (uint32_t)V, "step: token id outside the vocabulary");
+            row_base[i + 1] = row_base[i] + (size_t)e.n_want;
+        }
+        // the scheduler's cut: launches of at most Tmax packed tokens; an entry that does not fit goes on in the next launch
+        std::vector<Piece> cur;
+        int used = 0;
+        for (int i = 0; i < n; ++i) {
+            int off = 0;
+            while (off < ents[i].n) {
+                if (used == Tmax) { launch(ents, cur, row_base, logits_out); cur.clear(); used = 0; }
+                const int cnt = std::min(ents[i].n - off, Tmax - used);
+                cur.push_back({i, off, cnt});
+                used += cnt; off += cnt;
+            }
+        }
+        if (!cur.empty()) launch(ents, cur, row_base, logits_out);
+        if (tokens_out) {
+            std::vector<uint32_t> h(slots);
+            AHA_CUDA_CHECK(cudaMemcpyAsync(h.data(), d_tok, slots * sizeof(uint32_t), cudaMemcpyDeviceToHost, c.stream));
+            AHA_CUDA_CHECK(cudaStreamSynchronize(c.stream));
+            for (int i = 0; i < n; ++i) tokens_out[i] = ents[i].sample ? h[ents[i].slot] : 0u;
+            int err = 0;
+            AHA_CUDA_CHECK(cudaMemcpy(&err, d_sample_err, sizeof(int), cudaMemcpyDeviceToHost));
+            if (err) { cudaMemset(d_sample_err, 0, sizeof(int)); throw std::runtime_error("sampler: the token weights are all zero or not finite"); }
+        } else if (logits_out) {
+            AHA_CUDA_CHECK(cudaStreamSynchronize(c.stream));
+        }
+    }
+
+    void map_pages(int slot, int n_tokens) {
+        const int need = ceil_div(n_tokens, kPage);
+        std::vector<int>& tb = h_tables[slot];
+        const int first = (int)tb.size();
+        if (need <= first) return;
+        AHA_REQUIRE((size_t)(need - first) <= free_pages.size(), "the KV pool is exhausted: " + std::to_string(num_pages * kPage) + " tokens are held by live sequences");
+        while ((int)tb.size() < need) { tb.push_back(free_pages.back()); free_pages.pop_back(); }
+        AHA_CUDA_CHECK(cudaMemcpyAsync(d_tables + (size_t)slot * max_pages + first, tb.data() + first, (size_t)(need - first) * sizeof(int), cudaMemcpyHostToDevice, c.stream));
+        AHA_CUDA_CHECK(cudaStreamSynchronize(c.stream));   // pageable source
+    }
+
+    void launch(const SeqStepEntry* ents, const std::vector<Piece>& pieces, const std::vector<size_t>& row_base, float* logits_out) {
+        cudaStream_t st = c.stream;
+        const int E = (int)pieces.size();
+        int T = 0;
+        for (auto& p : pieces) T += p.cnt;
+        for (auto& p : pieces) map_pages(ents[p.ent].slot, seqs[ents[p.ent].slot].pos + p.cnt);
+        // ---- metadata: tokens | fb_slot | tok_entry | tok_pos | ent_start | ent_pos0 | ent_slot | rows
+        if (meta_pending) { AHA_CUDA_CHECK(cudaEventSynchronize(ev_meta)); meta_pending = false; }
+        int* hm = h_meta;
+        int* tokens = hm; int* fb = tokens + Tmax; int* tok_entry = fb + Tmax; int* tok_pos = tok_entry + Tmax;
+        int* ent_start = tok_pos + Tmax; int* ent_pos0 = ent_start + (slots + 1); int* ent_slot = ent_pos0 + slots; int* rows = ent_slot + slots;
+        struct OutRow { size_t out; };           // logits_out row of a wanted packed row
+        std::vector<size_t> want_out;
+        std::vector<int> sample_slots;
+        int t = 0, nrows = 0;
+        bool any_fb = false;
+        for (int i = 0; i < E; ++i) {
+            const Piece& p = pieces[i];
+            const SeqStepEntry& e = ents[p.ent];
+            const int pos0 = seqs[e.slot].pos;
+            ent_start[i] = t; ent_pos0[i] = pos0; ent_slot[i] = e.slot;
+            for (int k = 0; k < p.cnt; ++k) {
+                tokens[t + k] = e.tokens ? (int)e.tokens[p.off + k] : 0;
+                fb[t + k] = e.tokens ? -1 : e.slot;
+                any_fb = any_fb || !e.tokens;
+                tok_entry[t + k] = i; tok_pos[t + k] = pos0 + k;
+            }
+            for (int k = 0; k < e.n_want; ++k)
+                if (e.want[k] >= p.off && e.want[k] < p.off + p.cnt) { rows[nrows++] = t + e.want[k] - p.off; want_out.push_back(row_base[p.ent] + k); }
+            t += p.cnt;
+        }
+        ent_start[E] = T;
+        const int n_want_rows = nrows;
+        for (int i = 0, tt = 0; i < E; ++i) {     // sampled rows come after the wanted ones
+            const Piece& p = pieces[i];
+            const SeqStepEntry& e = ents[p.ent];
+            tt += p.cnt;
+            if (e.sample && p.off + p.cnt == e.n) { rows[nrows++] = tt - 1; sample_slots.push_back(e.slot); }
+        }
+        AHA_CUDA_CHECK(cudaMemcpyAsync(d_meta, h_meta, meta_ints * sizeof(int), cudaMemcpyHostToDevice, st));
+        AHA_CUDA_CHECK(cudaEventRecord(ev_meta, st));
+        meta_pending = true;
+        int* dm = d_meta;
+        RaggedBatch rb;
+        rb.T = T; rb.E = E;
+        rb.tokens = reinterpret_cast<const uint32_t*>(dm);
+        const int* d_fb = dm + Tmax;
+        rb.tok_entry = dm + 2 * Tmax; rb.tok_pos = dm + 3 * Tmax;
+        rb.ent_start = dm + 4 * Tmax; rb.ent_pos0 = rb.ent_start + (slots + 1); rb.ent_slot = rb.ent_pos0 + slots;
+        const int* d_rows = rb.ent_slot + slots;
+        rb.page_tables = d_tables; rb.max_pages = max_pages;
+        if (any_fb) { feedback_tokens_kernel<<<ceil_div(T, 256), 256, 0, st>>>(reinterpret_cast<uint32_t*>(dm), d_fb, d_states, T); c.cnt.kernels++; }
+        // ---- the layer stack
+        if (fp32) embed_gather_any_kernel<float><<<T, 128, 0, st>>>(rb.tokens, reinterpret_cast<const float*>(embed), x, W, V);
+        else embed_gather_any_kernel<__nv_bfloat16><<<T, 128, 0, st>>>(rb.tokens, reinterpret_cast<const __nv_bfloat16*>(embed), x, W, V);
+        c.cnt.kernels++;
+        StepView v{this, rb, x, y};
+        for (int l = 0; l < L; ++l) {
+            LayerRec& Ly = layers[l];
+            Ly.mixer->run(v);
+            scalar_rmsnorm_add_kernel<<<T, 256, 0, st>>>(x, y, Ly.gain1, eps, W); c.cnt.kernels++;
+            if (Ly.ff) {
+                Ly.ff->run(v);
+                scalar_rmsnorm_add_kernel<<<T, 256, 0, st>>>(x, y, Ly.gain2, eps, W); c.cnt.kernels++;
+            }
+            if (trace) AHA_CUDA_CHECK(cudaMemcpyAsync(trace_buf + (size_t)l * Tmax * W, x, (size_t)T * W * sizeof(float), cudaMemcpyDeviceToDevice, st));
+        }
+        trace_T = T;
+        AHA_CUDA_CHECK(cudaGetLastError());
+        // ---- final norm + head for the wanted / sampled rows, Rmax rows at a time
+        for (int r0 = 0; r0 < nrows; r0 += Rmax) {
+            const int nr = std::min(Rmax, nrows - r0);
+            scalar_rmsnorm_rows_kernel<<<nr, 256, 0, st>>>(x, d_rows + r0, final_gain, eps, hn, W); c.cnt.kernels++;
+            gemm(AEPI_STORE, hn, W, head, logits, V, nr);
+            for (int r = 0; r < nr; ++r) {
+                const int gr = r0 + r;
+                const float* lg = logits + (size_t)r * V;
+                if (gr < n_want_rows) {
+                    if (logits_out) AHA_CUDA_CHECK(cudaMemcpyAsync(logits_out + want_out[gr] * (size_t)V, lg, (size_t)V * sizeof(float), cudaMemcpyDeviceToHost, st));
+                } else {
+                    const int slot = sample_slots[gr - n_want_rows];
+                    argmax_partial_kernel<<<n_pcand, 256, 0, st>>>(lg, V, pmax, pidx);
+                    argmax_final_kernel<<<1, 32, 0, st>>>(pmax, pidx, n_pcand, d_tok + slot, d_states + slot, d_hist + (size_t)slot * hist_cap, hist_cap, 1);
+                    c.cnt.kernels += 2;
+                    if (seqs[slot].samp_active) {   // the sampled token replaces the ArgMax one that was just pushed
+                        SampleArgs a = seqs[slot].samp;
+                        a.logits = lg;
+                        sample_kernel<<<1, kSampleThreads, 0, st>>>(a);
+                        c.cnt.kernels++;
+                    }
+                }
+            }
+            if (r0 + nr < nrows) AHA_CUDA_CHECK(cudaStreamSynchronize(st));   // the logits buffer is reused by the next chunk only after its copies have left
+        }
+        AHA_CUDA_CHECK(cudaGetLastError());
+        for (auto& p : pieces) seqs[ents[p.ent].slot].pos += p.cnt;
+    }
+
+    void bench(const char*, int, int, int, double*, uint64_t*, uint64_t*) override { throw std::runtime_error("seq engine: kernel bench not available"); }
+};
+
+// ------------------------------------------------------------------------------------------------------------------------------
+struct Hgrn2Mixer final : Sublayer {
+    Engine& E;
+    int H, D, Dv;
+    LinearAny in, out;
+    float *lower = nullptr, *norm_w = nullptr, *state = nullptr;
+    size_t slot_stride = 0;
+    Hgrn2Mixer(Engine& e, const Json& mx, const WeightTable& wt, const std::string& p) : E(e) {
+        H = mx.integer("heads"); D = mx.integer("dim"); Dv = mx.integer("vdim");
+        AHA_REQUIRE(H >= 1 && D >= 1 && Dv >= 1, "hgrn2: bad sizes");
+        in = E.load_linear(wt, {p + "q", p + "f", p + "v"}, {H * D, H * D, H * Dv}, E.W, {"", p + "f.b", ""});
+        out = E.load_linear(wt, {p + "o"}, {E.W}, H * Dv, {});
+        lower = upload_vec(E.c, wt, p + "lower", (size_t)H * D);
+        norm_w = upload_vec(E.c, wt, p + "norm", (size_t)Dv);
+        slot_stride = (size_t)H * D * Dv;
+        state = E.c.alloc<float>(slot_stride * E.slots);
+        AHA_CUDA_CHECK(cudaMemset(state, 0, slot_stride * E.slots * sizeof(float)));
+        const size_t smem = hgrn2_scan_smem(D, Dv);
+        AHA_REQUIRE(smem <= 200 * 1024, "hgrn2: dim x vdim state does not fit shared memory");
+        AHA_CUDA_CHECK(cudaFuncSetAttribute(hgrn2_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    }
+    int proj_cols() const override { return in.N; }
+    int inner_cols() const override { return H * Dv; }
+    void run(const StepView& v) override {
+        const int T = v.rb.T;
+        E.gemm(AEPI_STORE, v.x, E.W, in, E.proj, in.N, T);
+        Hgrn2Args a{};
+        a.qfv = E.proj; a.ld = in.N; a.lower = lower; a.norm_w = norm_w; a.eps = E.eps; a.state = state; a.slot_stride = slot_stride;
+        a.out = E.inner; a.H = H; a.D = D; a.Dv = Dv; a.rb = v.rb;
+        hgrn2_scan(E.c.stream, a); E.c.cnt.kernels++;
+        E.gemm(AEPI_STORE, E.inner, H * Dv, out, v.y, E.W, T);
+    }
+};
+
+struct WindowAttentionMixer final : Sublayer {
+    Engine& E;
+    int H, G, D, Dv, taps = 0, window = 0, kv_from = -1;
+    float scale = 1.f;
+    LinearAny in, out;
+    int q_off = 0, k_off = 0, v_off = 0, g_off = -1;
+    float *wq = nullptr, *wk = nullptr, *wv = nullptr, *q_norm = nullptr, *k_norm = nullptr, *slopes = nullptr, *tails = nullptr;
+    size_t tail_stride = 0;
+    PagedKV kv;          // own pages, or the owner's when kv_from >= 0
+    bool owns_kv = true;
+    WindowAttentionMixer(Engine& e, const Json& mx, const WeightTable& wt, const std::string& p, int layer_index) : E(e) {
+        H = mx.integer("heads"); G = mx.integer_or("kv_heads", H); D = mx.integer("dim"); Dv = mx.integer_or("vdim", D);
+        AHA_REQUIRE(H >= 1 && G >= 1 && H % G == 0, "attention: heads must be a multiple of kv_heads");
+        scale = (float)mx.number("scale");
+        taps = mx.integer_or("conv", 0);
+        window = mx.has("mask") ? mx.at("mask").integer("size") : 0;
+        AHA_REQUIRE(window >= 0, "attention: mask.size must be positive");
+        kv_from = mx.integer_or("kv_from", -1);
+        owns_kv = kv_from < 0;
+        const bool gate = wt.has(p + "g");
+        std::vector<std::string> names{p + "q"}, biases{p + "q.b"};
+        std::vector<int> rows{H * D};
+        int col = H * D;
+        if (owns_kv) {
+            k_off = col; names.push_back(p + "k"); biases.push_back(p + "k.b"); rows.push_back(G * D); col += G * D;
+            v_off = col; names.push_back(p + "v"); biases.push_back(p + "v.b"); rows.push_back(G * Dv); col += G * Dv;
+        }
+        if (gate) { g_off = col; names.push_back(p + "g"); biases.push_back(""); rows.push_back(H * Dv); col += H * Dv; }
+        in = E.load_linear(wt, names, rows, E.W, biases);
+        out = E.load_linear(wt, {p + "o"}, {E.W}, H * Dv, {});
+        if (wt.has(p + "q.norm")) q_norm = upload_vec(E.c, wt, p + "q.norm", (size_t)H * D);
+        if (owns_kv && wt.has(p + "k.norm")) k_norm = upload_vec(E.c, wt, p + "k.norm", (size_t)G * D);
+        if (taps > 1) {
+            AHA_REQUIRE(taps <= kConvMaxTaps, "attention: conv has more than 16 taps");
+            wq = upload_vec(E.c, wt, p + "q.conv", (size_t)H * D * taps);
+            if (owns_kv) { wk = upload_vec(E.c, wt, p + "k.conv", (size_t)G * D * taps); wv = upload_vec(E.c, wt, p + "v.conv", (size_t)G * Dv * taps); }
+            tail_stride = (size_t)(taps - 1) * (H * D + (owns_kv ? G * D + G * Dv : 0));
+            tails = E.c.alloc<float>(tail_stride * E.slots);
+            AHA_CUDA_CHECK(cudaMemset(tails, 0, tail_stride * E.slots * sizeof(float)));
+        }
+        std::vector<float> sl(H);
+        for (int h = 0; h < H; ++h) sl[h] = (float)std::exp2(-8.0 * (double)(h + 1) / (double)H);
+        slopes = upload(E.c, sl);
+        if (owns_kv) {
+            kv.G = G; kv.D = D; kv.Dv = Dv;
+            const size_t nk = (size_t)E.num_pages * G * kPage * D, nv = (size_t)E.num_pages * G * kPage * Dv;
+            kv.k = E.c.alloc<float>(nk); kv.v = E.c.alloc<float>(nv);
+            AHA_CUDA_CHECK(cudaMemset(kv.k, 0, nk * sizeof(float)));
+            AHA_CUDA_CHECK(cudaMemset(kv.v, 0, nv * sizeof(float)));
+        } else {
+            AHA_REQUIRE(kv_from < layer_index, "attention: kv_from must name an earlier layer");
+            auto* src = dynamic_cast<WindowAttentionMixer*>(E.mixer_of_layer[kv_from]);
+            AHA_REQUIRE(src && src->owns_kv, "attention: kv_from must name an attention layer with keys and values of its own");
+            AHA_REQUIRE(src->G == G && src->D == D && src->Dv == Dv, "attention: kv_from layer has other key / value sizes");
+            kv = src->kv;
+        }
+    }
+    int proj_cols() const override { return in.N; }
+    int inner_cols() const override { return H * Dv; }
+    int q_cols() const override { return H * D; }
+    uint64_t kv_bytes_per_token() const override { return owns_kv ? 4ull * G * (D + Dv) : 0; }
+    void run(const StepView& v) override {
+        const int T = v.rb.T;
+        E.gemm(AEPI_STORE, v.x, E.W, in, E.proj, in.N, T);
+        QkvPrepArgs a{};
+        a.proj = E.proj; a.ld = in.N; a.q_off = q_off; a.k_off = k_off; a.v_off = v_off;
+        a.Cq = H * D; a.Ck = owns_kv ? G * D : 0; a.Cv = owns_kv ? G * Dv : 0;
+        a.taps = taps; a.wq = wq; a.wk = wk; a.wv = wv; a.tails = tails; a.tail_slot_stride = tail_stride;
+        a.q_norm = q_norm; a.k_norm = k_norm; a.eps = E.eps; a.q_out = E.qbuf; a.kv = kv; a.rb = v.rb;
+        qkv_prepare(E.c.stream, a); E.c.cnt.kernels += taps > 1 ? 2 : 1;
+        WindowAttnArgs w{};
+        w.q = E.qbuf; w.kv = kv; w.slopes = slopes; w.scale = scale; w.window = window;
+        w.gate = g_off >= 0 ? E.proj + g_off : nullptr; w.gate_ld = in.N; w.out = E.inner; w.H = H; w.rb = v.rb;
+        window_attn(E.c.stream, w); E.c.cnt.kernels++;
+        E.gemm(AEPI_STORE, E.inner, H * Dv, out, v.y, E.W, T);
+    }
+};
+
+struct DenseFF final : Sublayer {
+    Engine& E;
+    int ff;
+    LinearAny up, down;
+    float alpha_p = 0.f, alpha_n = 0.f;
+    DenseFF(Engine& e, const Json& cfg, const WeightTable& wt, const std::string& p) : E(e) {
+        ff = cfg.integer("ff");
+        up = E.load_linear(wt, {p + "up"}, {ff}, E.W, {});
+        down = E.load_linear(wt, {p + "down"}, {E.W}, ff, {});
+        auto a = wt.vec_f32(p + "act", 2);
+        alpha_p = (float)softplus_d(a[0]);
+        alpha_n = (float)(0.5 + softplus_d(a[1]));
+    }
+    int proj_cols() const override { return ff; }
+    int inner_cols() const override { return 0; }
+    void run(const StepView& v) override {
+        E.gemm(AEPI_XIELU, v.x, E.W, up, E.proj, ff, v.rb.T, alpha_p, alpha_n);
+        E.gemm(AEPI_STORE, E.proj, ff, down, v.y, E.W, v.rb.T);
+    }
+};
+
+using MixerFactory = std::function<std::unique_ptr<Sublayer>(Engine&, const Json&, const WeightTable&, const std::string&, int)>;
+const std::map<std::string, MixerFactory>& mixer_registry() {
+    static const std::map<std::string, MixerFactory> r = {
+        {"hgrn2", [](Engine& e, const Json& mx, const WeightTable& wt, const std::string& p, int) { return std::unique_ptr<Sublayer>(new Hgrn2Mixer(e, mx, wt, p)); }},
+        {"attention", [](Engine& e, const Json& mx, const WeightTable& wt, const std::string& p, int l) { return std::unique_ptr<Sublayer>(new WindowAttentionMixer(e, mx, wt, p, l)); }},
+    };
+    return r;
+}
+using FFFactory = std::function<std::unique_ptr<Sublayer>(Engine&, const Json&, const WeightTable&, const std::string&)>;
+const std::map<std::string, FFFactory>& ff_registry() {
+    static const std::map<std::string, FFFactory> r = {
+        {"dense", [](Engine& e, const Json& cfg, const WeightTable& wt, const std::string& p) { return std::unique_ptr<Sublayer>(new DenseFF(e, cfg, wt, p)); }},
+    };
+    return r;
+}
+
+float* upload_scalar(Engine& E, const WeightTable& wt, const std::string& name) { return upload_vec(E.c, wt, name, 1); }
+
+}  // namespace
+
+SeqEngine* make_layered_engine(Ctx& ctx, const Json& cfg, const WeightTable& wt, const SeqEngineOptions& opt) {
+    std::unique_ptr<Engine> E(new Engine(ctx, opt));
+    Engine& e = *E;
+    const size_t before = ctx.alloc_bytes;
+    e.fp32 = opt.fp32;
+    e.W = cfg.integer("width"); e.V = cfg.integer("vocab");
+    e.eps = (float)cfg.at("norm").number("eps");
+    const Json& ls = cfg.at("layers");
+    AHA_REQUIRE(ls.kind == Json::Arr && !ls.arr.empty(), "config.json: 'layers' must be a non-empty list");
+    e.L = (int)ls.arr.size();
+    e.slots = std::max(1, opt.max_seqs);
+    e.num_pages = std::max(1, ceil_div(std::max(1, opt.max_tokens), kPage));
+    e.max_pages = e.num_pages;
+    e.Tmax = std::max(1, opt.max_step_tokens);
+    e.Rmax = std::min(e.Tmax, 128);
+    e.embed = e.load_linear(wt, {"embed"}, {e.V}, e.W, {}).w;
+    e.head = e.load_linear(wt, {"head"}, {e.V}, e.W, {});
+    e.final_gain = upload_scalar(e, wt, "final.norm");
+    int proj_cols = 1, inner_cols = 1, q_cols = 1;
+    for (int l = 0; l < e.L; ++l) {
+        const Json& ly = ls.arr[l];
+        const std::string p = "l" + std::to_string(l) + ".";
+        const std::string type = ly.string_or("type", "");
+        auto it = mixer_registry().find(type);
+        AHA_REQUIRE(it != mixer_registry().end(), "config.json: layer " + std::to_string(l) + " has an unknown mixer type '" + type + "'");
+        Engine::LayerRec rec;
+        rec.mixer = it->second(e, ly.at("mixer"), wt, p + "mix.", l);
+        e.mixer_of_layer.push_back(rec.mixer.get());
+        rec.gain1 = upload_scalar(e, wt, p + "norm1");
+        if (ly.has("mlp")) {
+            const Json& ml = ly.at("mlp");
+            const std::string kind = ml.string_or("kind", "");
+            auto jt = ff_registry().find(kind);
+            AHA_REQUIRE(jt != ff_registry().end(), "config.json: layer " + std::to_string(l) + " has an unknown feed-forward kind '" + kind + "'");
+            rec.ff = jt->second(e, ml, wt, p + "mlp.");
+            rec.gain2 = upload_scalar(e, wt, p + "norm2");
+        }
+        for (Sublayer* s : {rec.mixer.get(), rec.ff.get()})
+            if (s) { proj_cols = std::max(proj_cols, s->proj_cols()); inner_cols = std::max(inner_cols, s->inner_cols()); q_cols = std::max(q_cols, s->q_cols()); }
+        e.layers.push_back(std::move(rec));
+    }
+    e.wbytes = ctx.alloc_bytes - before;
+    // pools and scratch
+    for (int p = 0; p < e.num_pages; ++p) e.free_pages.push_back(p);
+    e.h_tables.resize(e.slots);
+    e.seqs.resize(e.slots);
+    e.d_tables = ctx.alloc<int>((size_t)e.slots * e.max_pages);
+    AHA_CUDA_CHECK(cudaMemset(e.d_tables, 0, (size_t)e.slots * e.max_pages * sizeof(int)));
+    const size_t T = e.Tmax;
+    e.x = ctx.alloc<float>(T * e.W); e.y = ctx.alloc<float>(T * e.W);
+    e.proj = ctx.alloc<float>(T * proj_cols); e.inner = ctx.alloc<float>(T * inner_cols); e.qbuf = ctx.alloc<float>(T * q_cols);
+    e.hn = ctx.alloc<float>((size_t)e.Rmax * e.W); e.logits = ctx.alloc<float>((size_t)e.Rmax * e.V);
+    e.meta_ints = 4 * T + (e.slots + 1) + 2 * e.slots + (T + e.slots);
+    e.d_meta = ctx.alloc<int>(e.meta_ints);
+    AHA_CUDA_CHECK(cudaMallocHost(&e.h_meta, e.meta_ints * sizeof(int)));
+    std::memset(e.h_meta, 0, e.meta_ints * sizeof(int));
+    AHA_CUDA_CHECK(cudaEventCreateWithFlags(&e.ev_meta, cudaEventDisableTiming));
+    e.hist_cap = std::max(64, e.num_pages * kPage);
+    e.d_states = ctx.alloc<DecodeState>(e.slots);
+    AHA_CUDA_CHECK(cudaMemset(e.d_states, 0, e.slots * sizeof(DecodeState)));
+    e.d_hist = ctx.alloc<uint32_t>((size_t)e.slots * e.hist_cap);
+    e.d_tok = ctx.alloc<uint32_t>(e.slots);
+    AHA_CUDA_CHECK(cudaMemset(e.d_tok, 0, e.slots * sizeof(uint32_t)));
+    e.pmax = ctx.alloc<float>(e.n_pcand); e.pidx = ctx.alloc<int>(e.n_pcand);
+    e.sample_work = ctx.alloc<float>((size_t)e.V);
+    e.d_sample_err = ctx.alloc<int>(1);
+    AHA_CUDA_CHECK(cudaMemset(e.d_sample_err, 0, sizeof(int)));
+    return E.release();
+}
+
+}  // namespace aha

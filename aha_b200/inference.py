@@ -72,7 +72,10 @@ def mm_fingerprint(data):
 
 class B200Model:
     def __init__(self, kind, config, weights, eos_ids=(), device=0, max_ctx=8192, max_prefill=0, max_patches=0,
-                 max_frames=0, use_graph=True, decode_impl=0, gemm_impl=0, attn_impl=0, tp_rank=0, tp_world=1, tp_unique_id=None):
+                 max_frames=0, use_graph=True, decode_impl=0, gemm_impl=0, attn_impl=0, tp_rank=0, tp_world=1, tp_unique_id=None,
+                 exact_fp32=False, max_seqs=0):
+        """kind "malasun": a layered-engine handle (config lists its layers); max_ctx = KV pool in tokens, max_prefill = tokens per
+        launch, max_seqs = state slots (0 = 8), exact_fp32 = every product in fp32 instead of bf16 weights."""
         self._lib = L.load()
         self.kind = kind
         self.config = config
@@ -86,6 +89,8 @@ class B200Model:
                          max_patches=max_patches, max_frames=max_frames, use_graph=1 if use_graph else 0,
                          decode_impl=decode_impl, gemm_impl=gemm_impl)
         opts.reserved[0] = attn_impl
+        opts.reserved[1] = 1 if exact_fp32 else 0
+        opts.reserved[2] = max_seqs
         if tp_world > 1:
             if tp_unique_id is None or len(tp_unique_id) != 128:
                 raise ValueError("tp_world > 1 needs the 128-byte NCCL unique id (nccl_unique_id() on rank 0, then broadcast)")
@@ -97,9 +102,12 @@ class B200Model:
         if rc != 0:
             raise B200Error(self._lib.aha_b200_last_error(None).decode())
         self._h = h
-        tc = config if kind == "qwen3" else (config["text_config"] if kind == "qwen3vl" else config["thinker_config"]["text_config"])
-        self.vocab_size = tc["vocab_size"]
-        self.hidden_size = tc["hidden_size"]
+        if kind in ("malasun", "layered"):
+            self.vocab_size, self.hidden_size = config["vocab"], config["width"]
+        else:
+            tc = config if kind == "qwen3" else (config["text_config"] if kind == "qwen3vl" else config["thinker_config"]["text_config"])
+            self.vocab_size = tc["vocab_size"]
+            self.hidden_size = tc["hidden_size"]
 
     # ------------------------------------------------------------------ helpers
     def _check(self, rc):
@@ -262,6 +270,40 @@ class B200Model:
 
     def batch_close(self):
         self._check(self._lib.aha_b200_batch_close(self._h))
+
+    # ------------------------------------------------------------------ layered engine: explicit sequences and the ragged step
+    def seq_open(self):
+        """A free sequence slot (position 0)."""
+        s = C.c_int32(-1)
+        self._check(self._lib.aha_b200_seq_open(self._h, C.byref(s)))
+        return s.value
+
+    def seq_close(self, slot):
+        self._check(self._lib.aha_b200_seq_close(self._h, slot))
+
+    def seq_info(self, slot=-1):
+        pos, free, ns = C.c_int64(0), C.c_int64(0), C.c_int32(0)
+        self._check(self._lib.aha_b200_seq_info(self._h, slot, C.byref(pos), C.byref(free), C.byref(ns)))
+        return {"position": pos.value, "free_tokens": free.value, "max_seqs": ns.value}
+
+    def feed(self, entries):
+        """One engine step.  entries: [(slot, token ids, wanted entry-local indices)], any mix of prompt portions and single tokens.
+        Returns the logits of the wanted positions in entry order, float32 [rows, vocab]."""
+        keep, arr = [], (L.FeedEntry * len(entries))()
+        rows = 0
+        for i, (slot, ids, want) in enumerate(entries):
+            ids = self._ids(ids)
+            want = np.ascontiguousarray(np.asarray(list(want), dtype=np.int32))
+            keep += [ids, want]
+            arr[i].slot = slot
+            arr[i].ids = ids.ctypes.data_as(C.POINTER(C.c_uint32))
+            arr[i].n = len(ids)
+            arr[i].want = want.ctypes.data_as(C.POINTER(C.c_int32))
+            arr[i].n_want = len(want)
+            rows += len(want)
+        out = np.empty((max(rows, 1), self.vocab_size), np.float32)
+        self._check(self._lib.aha_b200_seq_feed(self._h, arr, len(entries), out.ctypes.data_as(C.POINTER(C.c_float)), rows))
+        return out[:rows]
 
     def generate_stream(self, input_ids, on_token, data=None, max_tokens=1024, temperature=0.0, top_p=None, top_k=None,
                         repeat_penalty=1.0, repeat_last_n=64, seed=299792458, reuse_prefix=False):

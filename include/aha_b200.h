@@ -31,7 +31,7 @@
 extern "C" {
 #endif
 
-#define AHA_B200_ABI_VERSION 3
+#define AHA_B200_ABI_VERSION 4
 
 typedef struct aha_model aha_model;
 
@@ -121,7 +121,7 @@ typedef struct aha_stats {
 
 /* XModel::new(cfg, VarBuilder, eos_ids) inside XGenerateModel::init
  * (/root/reference/src/models/qwen3/generate.rs:22-50, qwen3vl/generate.rs:33-63,
- *  qwen3_asr/generate.rs:51-87).  kind = "qwen3" | "qwen3vl" | "qwen3_asr"; config_json is the
+ *  qwen3_asr/generate.rs:51-87).  kind = "qwen3" | "qwen3vl" | "qwen3_asr" | "malasun" (layered engine, below); config_json is the
  * checkpoint's config.json text; weights are the safetensors tensors by name. */
 int aha_b200_create(const char* kind, const char* config_json,
                     const aha_tensor_desc* weights, size_t n_weights,
@@ -290,6 +290,34 @@ int aha_b200_embed(aha_model* m, const uint32_t* ids, size_t seq_len, float* out
  * doc_lens[n_docs] their lengths; scores_out: n_docs floats. */
 int aha_b200_rerank(aha_model* m, const uint32_t* query_ids, size_t query_len, const uint32_t* doc_ids, const size_t* doc_lens,
                     size_t n_docs, float* scores_out);
+
+/* ---- layered sequence engine (new design; nothing like it in the reference) ----------------------------------------------------
+ * kind = "malasun" creates a handle for a model whose config.json LISTS its layers (config "layers": per layer a mixer type -- gated linear
+ * recurrence "hgrn2" or windowed "attention" -- with its sizes and constants, and an optional feed-forward).  Such a handle is served by one
+ * ragged step function: any mix of prompt portions and single tokens of different sequences in one step, over a paged KV pool
+ * (aha_options.max_ctx tokens, 32-token pages from one free list) and aha_options.reserved[2] state slots (0 = 8; recurrent state,
+ * convolution tails and sampler state of a sequence).  aha_options.reserved[1] = 1 selects exact fp32 arithmetic everywhere (weights widened
+ * to fp32); 0 is the serving mode (bf16 weights, fp32 accumulation, fp32 residual / norms / gates / states / softmax).
+ * aha_options.max_prefill = tokens per launch; a longer step is cut into portions by the engine.
+ * All entries above that make sense for it work on such a handle (forward_initial / _step / _extend on one sequence, generate, generate_stream,
+ * generate_batch -- all prompts in ONE step --, batch_open / _add / _step / _close, clear_cache, set_trace + debug_read("hidden")).  The three
+ * below drive the step function directly (a scheduler or a trace replay):
+ *   seq_open   -> a free slot, at position 0            seq_close(slot): its pages and the slot are free again
+ *   seq_feed   one step: every entry appends n ids to its slot's sequence; `want` lists (ascending) the entry-local indices whose logits are
+ *              asked for; logits_out receives them in entry order, [rows][vocab].  The result for a position does not depend on how the
+ *              sequence was cut into steps, on the other entries, or on which pages / slot it uses, beyond fp32 rounding. */
+typedef struct aha_feed_entry {
+    int32_t slot;
+    const uint32_t* ids;
+    size_t n;
+    const int32_t* want;
+    size_t n_want;
+} aha_feed_entry;
+int aha_b200_seq_open(aha_model* m, int32_t* slot_out);
+int aha_b200_seq_close(aha_model* m, int32_t slot);
+int aha_b200_seq_feed(aha_model* m, const aha_feed_entry* entries, size_t n, float* logits_out, size_t cap_rows);
+/* position of a slot (slot < 0: skipped), unmapped KV capacity in tokens, number of slots; any pointer may be NULL */
+int aha_b200_seq_info(aha_model* m, int32_t slot, int64_t* position_out, int64_t* free_tokens_out, int32_t* max_seqs_out);
 
 /* Tensor parallelism (new design; the reference has none): rank 0 creates a 128-byte ncclUniqueId, the host side
  * distributes it (bench.py broadcasts it between the per-GPU processes) and every rank passes it in aha_options.tp_comm together
