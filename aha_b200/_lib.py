@@ -87,6 +87,7 @@ SYMBOLS = {
     "aha_b200_seq_open": (C.c_int, [_P, C.POINTER(C.c_int32)]),
     "aha_b200_seq_close": (C.c_int, [_P, C.c_int32]),
     "aha_b200_seq_feed": (C.c_int, [_P, C.POINTER(FeedEntry), C.c_size_t, _F32P, C.c_size_t]),
+    "aha_b200_seq_profile": (C.c_int, [_P, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_char_p, C.c_size_t]),
     "aha_b200_seq_info": (C.c_int, [_P, C.c_int32, C.POINTER(C.c_int64), C.POINTER(C.c_int64), C.POINTER(C.c_int32)]),
     "aha_b200_generate_stream": (C.c_int, [_P, _U32P, C.c_size_t, C.POINTER(MM), C.POINTER(GenParams), TOKEN_CALLBACK, C.c_void_p,
                                            C.POINTER(Usage)]),

@@ -1755,6 +1755,17 @@ int aha_b200_seq_feed(aha_model* m, const aha_feed_entry* entries, size_t n, flo
         AHA_CUDA_CHECK(cudaStreamSynchronize(m->ctx.stream));
     });
 }
+int aha_b200_seq_profile(aha_model* m, int32_t n_seqs, int32_t tokens_per_seq, int32_t ctx, int32_t warmup, int32_t iters, char* json_out, size_t cap) {
+    return guarded(m, [&] {
+        AHA_REQUIRE(is_seq(m), "sequence entries need a layered-engine handle");
+        AHA_REQUIRE(json_out && cap > 0, "json_out is required");
+        require_no_session(m);
+        m->seq_single = -1;
+        const std::string j = m->seq->profile(n_seqs, tokens_per_seq, ctx, warmup, iters);
+        AHA_REQUIRE(j.size() + 1 <= cap, "json_out is too small");
+        std::memcpy(json_out, j.c_str(), j.size() + 1);
+    });
+}
 int aha_b200_seq_info(aha_model* m, int32_t slot, int64_t* position_out, int64_t* free_tokens_out, int32_t* max_seqs_out) {
     return guarded(m, [&] {
         AHA_REQUIRE(is_seq(m), "sequence entries need a layered-engine handle");

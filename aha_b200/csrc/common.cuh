@@ -97,7 +97,7 @@ __device__ __forceinline__ float xielu_f(float z, float alpha_p, float alpha_n) 
 }
 __device__ __forceinline__ float sigmoid_f(float x) { return 1.f / (1.f + expf(-x)); }
 
-enum Act { ACT_NONE = 0, ACT_SILU = 1, ACT_GELU_ERF = 2, ACT_GELU_TANH = 3 };
+enum Act { ACT_NONE = 0, ACT_SILU = 1, ACT_GELU_ERF = 2, ACT_GELU_TANH = 3, ACT_XIELU = 4 /* two parameters: callers use xielu_f */ };
 __device__ __forceinline__ float apply_act(int act, float x) {
     switch (act) {
         case ACT_SILU: return silu_f(x);

@@ -82,40 +82,82 @@ static __global__ void __launch_bounds__(256) gemm_any_kernel(GemmAnyArgs g) {
     }
 }
 
-// M <= MB rows.  Warp w of the grid owns output columns w, w + warps, ...; lane l multiplies elements l, l + 32, ... of the weight row with
-// the same elements of every activation row (L1-resident), then the warp tree-sums.  The weight matrix is read exactly once per launch.
-template <typename WT, int EPI, int MB>
+// eight consecutive weights of a row as floats: one 16-byte streaming load for bf16, two for fp32
+__device__ __forceinline__ void load_w8(const __nv_bfloat16* p, float (&w)[8]) {
+    const uint4 u = ldg_stream(p);
+    const uint32_t v[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { w[2 * i] = __uint_as_float(v[i] << 16); w[2 * i + 1] = __uint_as_float(v[i] & 0xffff0000u); }
+}
+__device__ __forceinline__ void load_w8(const float* p, float (&w)[8]) {
+    const uint4 u0 = ldg_stream(p), u1 = ldg_stream(p + 4);
+    w[0] = __uint_as_float(u0.x); w[1] = __uint_as_float(u0.y); w[2] = __uint_as_float(u0.z); w[3] = __uint_as_float(u0.w);
+    w[4] = __uint_as_float(u1.x); w[5] = __uint_as_float(u1.y); w[6] = __uint_as_float(u1.z); w[7] = __uint_as_float(u1.w);
+}
+
+// M <= MB rows.  A warp owns two output columns at a time; lane l multiplies elements 8l .. 8l + 7 (+ 256, ...) of the two weight rows with
+// the same elements of every activation row (L1-resident), then the warp tree-sums.  The weight matrix is streamed exactly once per
+// launch with 16-byte loads (VEC: K % 8 == 0 and 16-byte aligned rows; otherwise element by element).
+template <typename WT, int EPI, int MB, bool VEC>
 static __global__ void __launch_bounds__(256) gemm_skinny_kernel(GemmAnyArgs g) {
     const WT* __restrict__ W = reinterpret_cast<const WT*>(g.W);
     const int lane = threadIdx.x & 31;
     const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, nwarps = (gridDim.x * blockDim.x) >> 5;
-    for (int n = warp; n < g.N; n += nwarps) {
-        const WT* wr = W + (size_t)n * g.K;
-        float acc[MB];
+    for (int n = warp * 2; n < g.N; n += nwarps * 2) {
+        const bool two = n + 1 < g.N;
+        const WT* w0 = W + (size_t)n * g.K;
+        const WT* w1 = W + (size_t)(two ? n + 1 : n) * g.K;
+        float acc0[MB], acc1[MB];
 #pragma unroll
-        for (int r = 0; r < MB; ++r) acc[r] = 0.f;
-        for (int k = lane; k < g.K; k += 32) {
-            const float w = wt_to_f(wr[k]);
+        for (int r = 0; r < MB; ++r) { acc0[r] = 0.f; acc1[r] = 0.f; }
+        if (VEC) {
+            for (int k = lane * 8; k < g.K; k += 256) {
+                float a[8], b[8];
+                load_w8(w0 + k, a);
+                load_w8(w1 + k, b);
 #pragma unroll
-            for (int r = 0; r < MB; ++r)
-                if (r < g.M) acc[r] = fmaf(g.A[(size_t)r * g.lda + k], w, acc[r]);
+                for (int r = 0; r < MB; ++r)
+                    if (r < g.M) {
+                        const float4 x0 = *reinterpret_cast<const float4*>(g.A + (size_t)r * g.lda + k);
+                        const float4 x1 = *reinterpret_cast<const float4*>(g.A + (size_t)r * g.lda + k + 4);
+                        const float x[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) { acc0[r] = fmaf(x[i], a[i], acc0[r]); acc1[r] = fmaf(x[i], b[i], acc1[r]); }
+                    }
+            }
+        } else {
+            for (int k = lane; k < g.K; k += 32) {
+                const float a = wt_to_f(w0[k]), b = wt_to_f(w1[k]);
+#pragma unroll
+                for (int r = 0; r < MB; ++r)
+                    if (r < g.M) { const float x = g.A[(size_t)r * g.lda + k]; acc0[r] = fmaf(x, a, acc0[r]); acc1[r] = fmaf(x, b, acc1[r]); }
+            }
         }
 #pragma unroll
         for (int r = 0; r < MB; ++r) {
-            const float v = warp_sum(acc[r]);
-            if (lane == 0 && r < g.M) g.C[(size_t)r * g.ldc + n] = any_epilogue<EPI>(g, v, n);
+            const float v0 = warp_sum(acc0[r]), v1 = warp_sum(acc1[r]);
+            if (lane == 0 && r < g.M) {
+                g.C[(size_t)r * g.ldc + n] = any_epilogue<EPI>(g, v0, n);
+                if (two) g.C[(size_t)r * g.ldc + n + 1] = any_epilogue<EPI>(g, v1, n + 1);
+            }
         }
     }
+}
+
+template <typename WT, int EPI, bool VEC>
+inline void gemm_skinny_launch(cudaStream_t st, const GemmAnyArgs& g, int num_sms) {
+    const int blocks = std::max(1, std::min(ceil_div(g.N, 16), num_sms * 8));
+    if (g.M <= 1) gemm_skinny_kernel<WT, EPI, 1, VEC><<<blocks, 256, 0, st>>>(g);
+    else if (g.M <= 2) gemm_skinny_kernel<WT, EPI, 2, VEC><<<blocks, 256, 0, st>>>(g);
+    else if (g.M <= 4) gemm_skinny_kernel<WT, EPI, 4, VEC><<<blocks, 256, 0, st>>>(g);
+    else gemm_skinny_kernel<WT, EPI, 8, VEC><<<blocks, 256, 0, st>>>(g);
 }
 
 template <typename WT, int EPI>
 inline void gemm_any_launch(cudaStream_t st, const GemmAnyArgs& g, int num_sms) {
     if (g.M <= 8) {
-        const int blocks = std::max(1, std::min(ceil_div(g.N, 8), num_sms * 8));
-        if (g.M <= 1) gemm_skinny_kernel<WT, EPI, 1><<<blocks, 256, 0, st>>>(g);
-        else if (g.M <= 2) gemm_skinny_kernel<WT, EPI, 2><<<blocks, 256, 0, st>>>(g);
-        else if (g.M <= 4) gemm_skinny_kernel<WT, EPI, 4><<<blocks, 256, 0, st>>>(g);
-        else gemm_skinny_kernel<WT, EPI, 8><<<blocks, 256, 0, st>>>(g);
+        const bool vec = g.K % 8 == 0 && g.lda % 4 == 0 && (reinterpret_cast<uintptr_t>(g.A) & 15) == 0 && (reinterpret_cast<uintptr_t>(g.W) & 15) == 0;
+        if (vec) gemm_skinny_launch<WT, EPI, true>(st, g, num_sms); else gemm_skinny_launch<WT, EPI, false>(st, g, num_sms);
     } else {
         gemm_any_kernel<WT, EPI><<<dim3(ceil_div(g.N, 64), ceil_div(g.M, 64)), 256, 0, st>>>(g);
     }

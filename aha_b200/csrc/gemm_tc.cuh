@@ -84,8 +84,11 @@ __device__ __forceinline__ uint64_t umma_desc_sw128(const void* smem_ptr) {
     d |= (uint64_t)2 << 61;
     return d;
 }
-// kind::f16 instruction descriptor: D=f32 (bit 4), A=B=f16 (0), both K-major, N>>3 at bit 17, M>>4 at bit 24.
-__device__ __forceinline__ uint32_t umma_idesc_f16(int M, int N) { return (1u << 4) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24); }
+// kind::f16 instruction descriptor: D=f32 (bit 4), A format at bit 7 and B format at bit 10 (0 = f16, 1 = bf16), both K-major, N>>3 at bit 17,
+// M>>4 at bit 24.
+__device__ __forceinline__ uint32_t umma_idesc_f16(int M, int N, int bf16 = 0) {
+    return (1u << 4) | (bf16 ? ((1u << 7) | (1u << 10)) : 0u) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
+}
 __device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
     asm volatile(
         "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
@@ -111,7 +114,7 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
 }
 
 // ------------------------------------------------------------------------------------------------ A = hi + lo split
-__global__ void split_f32_to_f16x2_kernel(const float* __restrict__ a, int lda, __half* __restrict__ hi, __half* __restrict__ lo, int M, int K) {
+static __global__ void split_f32_to_f16x2_kernel(const float* __restrict__ a, int lda, __half* __restrict__ hi, __half* __restrict__ lo, int M, int K) {
     const size_t i4 = (size_t)blockIdx.x * blockDim.x + threadIdx.x;   // index of a float4 inside [M, K]
     const size_t per_row = K / 4;
     if (i4 >= (size_t)M * per_row) return;
@@ -128,6 +131,24 @@ __global__ void split_f32_to_f16x2_kernel(const float* __restrict__ a, int lda, 
     *reinterpret_cast<uint2*>(lo + r * K + c) = make_uint2(*reinterpret_cast<uint32_t*>(&l[0]), *reinterpret_cast<uint32_t*>(&l[2]));
 }
 
+// the same split into bfloat16 halves (bf16 weights: hi + lo carries 16 significant bits of the activation)
+static __global__ void split_f32_to_bf16x2_kernel(const float* __restrict__ a, int lda, __nv_bfloat16* __restrict__ hi, __nv_bfloat16* __restrict__ lo, int M, int K) {
+    const size_t i4 = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t per_row = K / 4;
+    if (i4 >= (size_t)M * per_row) return;
+    const size_t r = i4 / per_row, c = (i4 % per_row) * 4;
+    const float4 v = *reinterpret_cast<const float4*>(a + r * lda + c);
+    const float x[4] = {v.x, v.y, v.z, v.w};
+    __nv_bfloat16 h[4], l[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+        h[e] = __float2bfloat16_rn(x[e]);
+        l[e] = __float2bfloat16_rn(x[e] - __bfloat162float(h[e]));
+    }
+    *reinterpret_cast<uint2*>(hi + r * K + c) = make_uint2(*reinterpret_cast<uint32_t*>(&h[0]), *reinterpret_cast<uint32_t*>(&h[2]));
+    *reinterpret_cast<uint2*>(lo + r * K + c) = make_uint2(*reinterpret_cast<uint32_t*>(&l[0]), *reinterpret_cast<uint32_t*>(&l[2]));
+}
+
 // ------------------------------------------------------------------------------------------------ the GEMM kernel
 struct GemmTcArgs {
     const float* bias;
@@ -138,6 +159,8 @@ struct GemmTcArgs {
     __half* out_hi = nullptr;   // when set, the result (after bias / activation / SwiGLU) is written as fp16 hi + lo halves [M, ldo] for the
     __half* out_lo = nullptr;   // next GEMM instead of fp32 C (EPI_STORE / EPI_ACT / EPI_SWIGLU)
     int ldo = 0;
+    int bf16 = 0;      // 1: A (hi / lo) and W hold bfloat16 instead of fp16 (same tiles and pipeline, the instruction descriptor names the format)
+    float act_a = 0.f, act_b = 0.f;   // ACT_XIELU: alpha_p, alpha_n
     int group_m = 8;   // persistent kernel: tiles are walked in bands of group_m row blocks (n outer, m inner) so that one wave of CTAs shares few A and W tiles
 };
 
@@ -178,7 +201,7 @@ __device__ __forceinline__ void tc_epilogue_store(const GemmTcArgs& g, float (&v
     }
     if (EPI == EPI_ACT) {
 #pragma unroll
-        for (int j = 0; j < 32; ++j) v[j] = apply_act(g.act, v[j]);
+        for (int j = 0; j < 32; ++j) v[j] = g.act == ACT_XIELU ? xielu_f(v[j], g.act_a, g.act_b) : apply_act(g.act, v[j]);
     }
     if (EPI == EPI_RESID) {
         const float* rr = g.resid + (size_t)row * g.ldr + n;
@@ -243,7 +266,7 @@ __global__ void __launch_bounds__(kTcThreads, kTcCtasPerSm) gemm_tc_kernel(const
         }
     } else if (warp == 1) {
         // ======================= MMA issuer
-        const uint32_t idesc = umma_idesc_f16(kTcBM, kTcBN);
+        const uint32_t idesc = umma_idesc_f16(kTcBM, kTcBN, g.bf16);
         for (int kb = 0; kb < nkb; ++kb) {
             const int s = kb % kTcStages;
             mbar_wait(&full[s], (kb / kTcStages) & 1);
@@ -351,7 +374,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc2_kernel(const __grid_co
         }
     } else if (warp == 1) {
         // ======================= MMA issuer
-        const uint32_t idesc = umma_idesc_f16(kTcBM, kTc2BN);
+        const uint32_t idesc = umma_idesc_f16(kTcBM, kTc2BN, g.bf16);
         int it = 0, ti = 0;
         for (int t = blockIdx.x; t < ntiles; t += gridDim.x, ++ti) {
             const int acc = ti & 1;
@@ -513,7 +536,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kTcThreads, 1)
     } else if (warp == 1) {
         // ======================= MMA issuer: the leader CTA only
         if (rank == 0) {
-            const uint32_t idesc = umma_idesc_f16(256, 256);
+            const uint32_t idesc = umma_idesc_f16(256, 256, g.bf16);
             int it = 0, ti = 0;
             for (int t = pair; t < ntiles; t += npairs, ++ti) {
                 const int acc = ti & 1;

@@ -19,6 +19,7 @@
 
 #include "attention_window.cuh"
 #include "gemm_any.cuh"
+#include "gemm_tc.cuh"
 #include "json.hpp"
 #include "kernels_common.cuh"
 #include "recurrence.cuh"
@@ -34,7 +35,12 @@ struct LinearAny {
     void* w = nullptr;    // [N, K] bf16 or fp32
     float* b = nullptr;   // [N] or nullptr
     int N = 0, K = 0;
+    CUtensorMap tmap, tmap256;   // TMA descriptors of the bf16 matrix for the tcgen05 kernels (128- and 256-row boxes), built on first use
+    bool has_tmap = false, has_tmap256 = false;
 };
+
+constexpr int kTcMinRows = 32;    // fewer rows than this run on the CUDA cores (a 128-row tensor-core tile would be mostly padding)
+constexpr int kGraphMaxTokens = 8;   // launches of at most this many tokens (decode steps) are replayed from CUDA graphs
 
 struct Engine;
 
@@ -74,7 +80,7 @@ struct Engine final : SeqEngine {
     std::vector<int> free_pages;
     std::vector<std::vector<int>> h_tables;   // [slot][mapped pages]
     int* d_tables = nullptr;
-    struct Seq { bool live = false; int pos = 0; bool samp_active = false; SampleArgs samp{}; };
+    struct Seq { bool live = false; int pos = 0; bool samp_active = false; SampleArgs samp{}; int samp_epoch = 0; };
     std::vector<Seq> seqs;
     // step scratch
     int Tmax = 0, Rmax = 0;
@@ -87,7 +93,35 @@ struct Engine final : SeqEngine {
     // trace
     bool trace = false; float* trace_buf = nullptr; int trace_T = 0;
 
+    // per-family device timing of a step (profile()): CUDA events around every launch family, summed over the layers
+    struct Prof { double ms = 0, flops = 0, bytes = 0; int launches = 0; };
+    bool profiling = false;
+    std::map<std::string, Prof> prof;
+    std::vector<cudaEvent_t> prof_ev;
+    struct ProfSpan { std::string name; size_t ev; double flops, bytes; };
+    std::vector<ProfSpan> prof_spans;
+    void tic(const char* name, double flops, double bytes) {
+        if (!profiling) return;
+        const size_t i = 2 * prof_spans.size();
+        while (prof_ev.size() < i + 2) { cudaEvent_t e; AHA_CUDA_CHECK(cudaEventCreate(&e)); prof_ev.push_back(e); }
+        AHA_CUDA_CHECK(cudaEventRecord(prof_ev[i], c.stream));
+        prof_spans.push_back({name, i, flops, bytes});
+    }
+    void toc() { if (profiling) AHA_CUDA_CHECK(cudaEventRecord(prof_ev[prof_spans.back().ev + 1], c.stream)); }
+    void prof_collect() {
+        AHA_CUDA_CHECK(cudaStreamSynchronize(c.stream));
+        for (auto& sp : prof_spans) {
+            float ms = 0.f;
+            AHA_CUDA_CHECK(cudaEventElapsedTime(&ms, prof_ev[sp.ev], prof_ev[sp.ev + 1]));
+            Prof& p = prof[sp.name];
+            p.ms += ms; p.flops += sp.flops; p.bytes += sp.bytes; p.launches += 1;
+        }
+        prof_spans.clear();
+    }
+
+    int sampler_epochs = 0;
     Engine(Ctx& ctx, const SeqEngineOptions& o) : c(ctx), opt(o) {}
+    ~Engine() override { clear_graphs(); for (auto e : prof_ev) cudaEventDestroy(e); if (h_meta) cudaFreeHost(h_meta); if (ev_meta) cudaEventDestroy(ev_meta); }
 
     // ---------------------------------------------------------------- weights
     // rows of several [N_i, K] tensors stacked into one matrix in the engine's storage type; absent bias parts are zeros
@@ -137,7 +171,38 @@ struct Engine final : SeqEngine {
         }
         return Lw;
     }
-    void gemm(int epi, const float* A, int lda, const LinearAny& Wt, float* C, int ldc, int M, float a0 = 0.f, float a1 = 0.f) {
+    // y = epilogue(x W^T + b).  Serving mode with enough rows and a shape that tiles: the library's tcgen05 kernels on bf16 operands -- the
+    // fp32 activations are split into bf16 hi + lo halves (16 significant bits), W is the bf16 checkpoint matrix, accumulation is fp32 in
+    // TMEM.  Otherwise (exact mode, decode steps, odd sizes): the CUDA-core kernels of gemm_any.cuh.
+    bool on_tensor_cores(int M, const LinearAny& Wt, int lda, int ldc) const {
+        return !fp32 && opt.gemm_impl != 1 && M >= kTcMinRows && gemm_tc_supported(M, Wt.N, Wt.K) && lda % 4 == 0 && ldc % 4 == 0;
+    }
+    void gemm(int epi, const float* A, int lda, LinearAny& Wt, float* C, int ldc, int M, float a0 = 0.f, float a1 = 0.f) {
+        tic(on_tensor_cores(M, Wt, lda, ldc) ? "linear (tcgen05, bf16 hi+lo)" : (M <= 8 ? "linear (decode rows, weights streamed once)" : "linear (CUDA cores)"),
+            2.0 * M * Wt.N * Wt.K, (double)Wt.N * Wt.K * (fp32 ? 4 : 2) + 4.0 * M * (Wt.K + Wt.N));
+        gemm_dispatch(epi, A, lda, Wt, C, ldc, M, a0, a1);
+        toc();
+    }
+    void gemm_dispatch(int epi, const float* A, int lda, LinearAny& Wt, float* C, int ldc, int M, float a0, float a1) {
+        if (on_tensor_cores(M, Wt, lda, ldc)) {
+            const size_t halfs = (size_t)M * Wt.K;
+            __half* hi = c.split_buf(halfs);
+            __half* lo = hi + c.split_cap;
+            split_f32_to_bf16x2_kernel<<<(unsigned)((halfs / 4 + 255) / 256), 256, 0, c.stream>>>(A, lda, reinterpret_cast<__nv_bfloat16*>(hi), reinterpret_cast<__nv_bfloat16*>(lo), M, Wt.K);
+            c.cnt.kernels++;
+            if (!Wt.has_tmap) { Wt.tmap = make_tmap_f16(Wt.w, (uint64_t)Wt.N, (uint64_t)Wt.K); Wt.has_tmap = true; }   // 16-bit elements: the copy is bitwise
+            GemmTcArgs t{};
+            t.bias = Wt.b; t.resid = nullptr; t.ldr = 0; t.C = C; t.ldc = ldc; t.M = M; t.N = Wt.N; t.K = Wt.K;
+            t.act = epi == AEPI_XIELU ? ACT_XIELU : ACT_NONE; t.act_a = a0; t.act_b = a1; t.bf16 = 1; t.group_m = std::max(1, c.gemm_group_m);
+            const int e = epi == AEPI_XIELU ? EPI_ACT : EPI_STORE;
+            if (c.gemm_pair && Wt.N >= 256 && M >= 1024) gemm_tc3_launch(c.stream, e, hi, lo, Wt.tmap, t, c.num_sms);
+            else if (c.gemm_wide && Wt.N >= 256) {
+                if (!Wt.has_tmap256) { Wt.tmap256 = make_tmap_f16_rows(Wt.w, (uint64_t)Wt.N, (uint64_t)Wt.K, 256); Wt.has_tmap256 = true; }
+                gemm_tc2_launch(c.stream, e, hi, lo, Wt.tmap256, t, c.num_sms);
+            } else gemm_tc_launch(c.stream, e, hi, lo, Wt.tmap, t);
+            c.cnt.kernels++;
+            return;
+        }
         GemmAnyArgs g{};
         g.A = A; g.lda = lda; g.W = Wt.w; g.bias = Wt.b; g.C = C; g.ldc = ldc; g.M = M; g.N = Wt.N; g.K = Wt.K; g.act_a = a0; g.act_b = a1;
         gemm_any(c.stream, epi, fp32, g, c.num_sms);
@@ -168,6 +233,7 @@ struct Engine final : SeqEngine {
     void set_sampler(int slot, const aha_gen_params& p) override {
         AHA_REQUIRE(live(slot), "sequence slot is not live");
         Seq& q = seqs[slot];
+        q.samp_epoch = ++sampler_epochs;
         const int mode = sampling_mode(p);
         const bool pen = !(p.repeat_penalty == 1.0f || p.repeat_last_n == 0);
         q.samp_active = mode != SAMPLE_ARGMAX || pen;
@@ -305,8 +371,51 @@ struct Engine final : SeqEngine {
         rb.ent_start = dm + 4 * Tmax; rb.ent_pos0 = rb.ent_start + (slots + 1); rb.ent_slot = rb.ent_pos0 + slots;
         const int* d_rows = rb.ent_slot + slots;
         rb.page_tables = d_tables; rb.max_pages = max_pages;
-        if (any_fb) { feedback_tokens_kernel<<<ceil_div(T, 256), 256, 0, st>>>(reinterpret_cast<uint32_t*>(dm), d_fb, d_states, T); c.cnt.kernels++; }
-        // ---- the layer stack
+        // ---- device work.  Decode-sized launches are replayed from a CUDA graph keyed by everything the launch arguments depend on.
+        const bool graphable = opt.use_graph && !trace && !profiling && T <= kGraphMaxTokens && nrows <= Rmax;
+        if (graphable) {
+            std::vector<int> key{T, E, n_want_rows, any_fb ? 1 : 0};
+            for (int sl : sample_slots) { key.push_back(sl); key.push_back(seqs[sl].samp_epoch); }
+            StepGraph* g = nullptr;
+            for (auto& e : graphs) if (e.key == key) { g = &e; break; }
+            if (!g) {
+                if (graphs.size() >= 64) clear_graphs();
+                const uint64_t k0 = c.cnt.kernels;
+                cudaGraph_t cg = nullptr;
+                AHA_CUDA_CHECK(cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal));
+                try { device_work(rb, d_fb, any_fb, d_rows, nrows, n_want_rows, sample_slots, nullptr, nullptr); }
+                catch (...) { cudaStreamEndCapture(st, &cg); if (cg) cudaGraphDestroy(cg); throw; }
+                AHA_CUDA_CHECK(cudaStreamEndCapture(st, &cg));
+                StepGraph e{key, nullptr, c.cnt.kernels - k0};
+                c.cnt.kernels = k0;
+                const cudaError_t err = cudaGraphInstantiate(&e.exec, cg, 0);
+                cudaGraphDestroy(cg);
+                AHA_CUDA_CHECK(err);
+                graphs.push_back(e);
+                g = &graphs.back();
+            }
+            AHA_CUDA_CHECK(cudaGraphLaunch(g->exec, st));
+            c.cnt.graphs++; c.cnt.kernels += g->kernels;
+            if (logits_out)
+                for (int r = 0; r < n_want_rows; ++r)
+                    AHA_CUDA_CHECK(cudaMemcpyAsync(logits_out + want_out[r] * (size_t)V, logits + (size_t)r * V, (size_t)V * sizeof(float), cudaMemcpyDeviceToHost, st));
+        } else {
+            device_work(rb, d_fb, any_fb, d_rows, nrows, n_want_rows, sample_slots, logits_out, &want_out);
+        }
+        for (auto& p : pieces) seqs[ents[p.ent].slot].pos += p.cnt;
+    }
+
+    struct StepGraph { std::vector<int> key; cudaGraphExec_t exec; uint64_t kernels; };
+    std::vector<StepGraph> graphs;
+    void clear_graphs() { for (auto& g : graphs) if (g.exec) cudaGraphExecDestroy(g.exec); graphs.clear(); }
+
+    // embed -> layers -> final norm + head (+ sampler) for `nrows` gathered rows.  want_out == nullptr (graph capture): no copies to the host and a
+    // single head chunk; else the wanted rows are copied out chunk by chunk.
+    void device_work(const RaggedBatch& rb, const int* d_fb, bool any_fb, const int* d_rows, int nrows, int n_want_rows, const std::vector<int>& sample_slots,
+                     float* logits_out, const std::vector<size_t>* want_out) {
+        cudaStream_t st = c.stream;
+        const int T = rb.T;
+        if (any_fb) { feedback_tokens_kernel<<<ceil_div(T, 256), 256, 0, st>>>(reinterpret_cast<uint32_t*>(d_meta), d_fb, d_states, T); c.cnt.kernels++; }
         if (fp32) embed_gather_any_kernel<float><<<T, 128, 0, st>>>(rb.tokens, reinterpret_cast<const float*>(embed), x, W, V);
         else embed_gather_any_kernel<__nv_bfloat16><<<T, 128, 0, st>>>(rb.tokens, reinterpret_cast<const __nv_bfloat16*>(embed), x, W, V);
         c.cnt.kernels++;
@@ -314,16 +423,19 @@ struct Engine final : SeqEngine {
         for (int l = 0; l < L; ++l) {
             LayerRec& Ly = layers[l];
             Ly.mixer->run(v);
+            tic("norm + residual", 4.0 * T * W, 12.0 * T * W);
             scalar_rmsnorm_add_kernel<<<T, 256, 0, st>>>(x, y, Ly.gain1, eps, W); c.cnt.kernels++;
+            toc();
             if (Ly.ff) {
                 Ly.ff->run(v);
+                tic("norm + residual", 4.0 * T * W, 12.0 * T * W);
                 scalar_rmsnorm_add_kernel<<<T, 256, 0, st>>>(x, y, Ly.gain2, eps, W); c.cnt.kernels++;
+                toc();
             }
             if (trace) AHA_CUDA_CHECK(cudaMemcpyAsync(trace_buf + (size_t)l * Tmax * W, x, (size_t)T * W * sizeof(float), cudaMemcpyDeviceToDevice, st));
         }
         trace_T = T;
         AHA_CUDA_CHECK(cudaGetLastError());
-        // ---- final norm + head for the wanted / sampled rows, Rmax rows at a time
         for (int r0 = 0; r0 < nrows; r0 += Rmax) {
             const int nr = std::min(Rmax, nrows - r0);
             scalar_rmsnorm_rows_kernel<<<nr, 256, 0, st>>>(x, d_rows + r0, final_gain, eps, hn, W); c.cnt.kernels++;
@@ -332,7 +444,7 @@ struct Engine final : SeqEngine {
                 const int gr = r0 + r;
                 const float* lg = logits + (size_t)r * V;
                 if (gr < n_want_rows) {
-                    if (logits_out) AHA_CUDA_CHECK(cudaMemcpyAsync(logits_out + want_out[gr] * (size_t)V, lg, (size_t)V * sizeof(float), cudaMemcpyDeviceToHost, st));
+                    if (logits_out) AHA_CUDA_CHECK(cudaMemcpyAsync(logits_out + (*want_out)[gr] * (size_t)V, lg, (size_t)V * sizeof(float), cudaMemcpyDeviceToHost, st));
                 } else {
                     const int slot = sample_slots[gr - n_want_rows];
                     argmax_partial_kernel<<<n_pcand, 256, 0, st>>>(lg, V, pmax, pidx);
@@ -349,10 +461,67 @@ struct Engine final : SeqEngine {
             if (r0 + nr < nrows) AHA_CUDA_CHECK(cudaStreamSynchronize(st));   // the logits buffer is reused by the next chunk only after its copies have left
         }
         AHA_CUDA_CHECK(cudaGetLastError());
-        for (auto& p : pieces) seqs[ents[p.ent].slot].pos += p.cnt;
     }
 
-    void bench(const char*, int, int, int, double*, uint64_t*, uint64_t*) override { throw std::runtime_error("seq engine: kernel bench not available"); }
+    int prof_n = 0, prof_tps = 0, prof_ctx = 0;   // shape of the profiled step
+    double prof_pairs(int window) const {          // (query, key) pairs an attention layer with this window visits
+        double k = 0;
+        for (int t = 0; t < prof_tps; ++t) k += window > 0 ? std::min(prof_ctx + t + 1, window) : prof_ctx + t + 1;
+        return k * prof_n;
+    }
+    double prof_unique(int window) const {         // distinct cached positions it reads
+        const int all = prof_ctx + prof_tps;
+        return (double)prof_n * (window > 0 ? std::min(all, window + prof_tps - 1) : all);
+    }
+
+    // Device-timed steps on synthetic tokens: n_seqs sequences, each feeding tokens_per_seq tokens at context ctx (positions are set, the cache holds
+    // whatever it holds: timing only).  Leaves every slot free.  Returns JSON.
+    std::string profile(int n_seqs, int tokens_per_seq, int ctx, int warmup, int iters) override {
+        AHA_REQUIRE(n_seqs >= 1 && n_seqs <= slots && tokens_per_seq >= 1 && ctx >= 0 && iters >= 1, "profile: bad arguments");
+        AHA_REQUIRE((size_t)n_seqs * ceil_div(ctx + tokens_per_seq, kPage) <= (size_t)num_pages, "profile: the KV pool is too small for this context");
+        release_all();
+        std::vector<std::vector<uint32_t>> toks(n_seqs);
+        std::vector<SeqStepEntry> ents(n_seqs);
+        for (int i = 0; i < n_seqs; ++i) {
+            ents[i].slot = admit();
+            toks[i].resize(tokens_per_seq);
+            for (int k = 0; k < tokens_per_seq; ++k) toks[i][k] = (uint32_t)((i * 7919 + k * 31 + 1) % V);
+            ents[i].tokens = toks[i].data(); ents[i].n = tokens_per_seq; ents[i].sample = true;
+            map_pages(ents[i].slot, ctx + tokens_per_seq);
+        }
+        std::vector<uint32_t> out(n_seqs);
+        auto one = [&] { for (auto& e : ents) seqs[e.slot].pos = ctx; step(ents.data(), n_seqs, nullptr, out.data()); };
+        cudaEvent_t e0, e1;
+        AHA_CUDA_CHECK(cudaEventCreate(&e0)); AHA_CUDA_CHECK(cudaEventCreate(&e1));
+        for (int i = 0; i < std::max(3, warmup); ++i) one();
+        const uint64_t k0 = c.cnt.kernels, g0 = c.cnt.graphs;
+        AHA_CUDA_CHECK(cudaEventRecord(e0, c.stream));
+        for (int i = 0; i < iters; ++i) one();
+        AHA_CUDA_CHECK(cudaEventRecord(e1, c.stream));
+        AHA_CUDA_CHECK(cudaEventSynchronize(e1));
+        float ms = 0.f;
+        AHA_CUDA_CHECK(cudaEventElapsedTime(&ms, e0, e1));
+        const double launches = (double)(c.cnt.kernels - k0) / iters, graphs_per = (double)(c.cnt.graphs - g0) / iters;
+        // the same steps with events around every launch family
+        prof.clear();
+        prof_n = n_seqs; prof_tps = tokens_per_seq; prof_ctx = ctx;
+        profiling = true;
+        const int pit = std::min(iters, 5);
+        try { for (int i = 0; i < pit; ++i) { one(); prof_collect(); } } catch (...) { profiling = false; prof_spans.clear(); throw; }
+        profiling = false;
+        release_all();
+        cudaEventDestroy(e0); cudaEventDestroy(e1);
+        std::string j = "{\"ms_per_step\": " + std::to_string(ms / iters) + ", \"tokens_per_step\": " + std::to_string(n_seqs * tokens_per_seq) +
+                        ", \"kernels_per_step\": " + std::to_string(launches) + ", \"graph_launches_per_step\": " + std::to_string(graphs_per) + ", \"families\": {";
+        bool first = true;
+        for (auto& kv : prof) {
+            if (!first) j += ", ";
+            first = false;
+            j += "\"" + kv.first + "\": {\"ms\": " + std::to_string(kv.second.ms / pit) + ", \"flops\": " + std::to_string(kv.second.flops / pit) + ", \"bytes\": " +
+                 std::to_string(kv.second.bytes / pit) + ", \"launches\": " + std::to_string(kv.second.launches / pit) + "}";
+        }
+        return j + "}}";
+    }
 };
 
 // ------------------------------------------------------------------------------------------------------------------------------
@@ -384,7 +553,9 @@ struct Hgrn2Mixer final : Sublayer {
         Hgrn2Args a{};
         a.qfv = E.proj; a.ld = in.N; a.lower = lower; a.norm_w = norm_w; a.eps = E.eps; a.state = state; a.slot_stride = slot_stride;
         a.out = E.inner; a.H = H; a.D = D; a.Dv = Dv; a.rb = v.rb;
+        E.tic("hgrn2 recurrence", 4.0 * T * H * D * Dv, 4.0 * T * (in.N + H * Dv) + 8.0 * v.rb.E * slot_stride);
         hgrn2_scan(E.c.stream, a); E.c.cnt.kernels++;
+        E.toc();
         E.gemm(AEPI_STORE, E.inner, H * Dv, out, v.y, E.W, T);
     }
 };
@@ -458,11 +629,15 @@ struct WindowAttentionMixer final : Sublayer {
         a.Cq = H * D; a.Ck = owns_kv ? G * D : 0; a.Cv = owns_kv ? G * Dv : 0;
         a.taps = taps; a.wq = wq; a.wk = wk; a.wv = wv; a.tails = tails; a.tail_slot_stride = tail_stride;
         a.q_norm = q_norm; a.k_norm = k_norm; a.eps = E.eps; a.q_out = E.qbuf; a.kv = kv; a.rb = v.rb;
+        E.tic("conv + q/k norm + cache write", 2.0 * T * (a.Cq + a.Ck + a.Cv) * std::max(1, taps), 4.0 * T * (2.0 * a.Cq + 2.0 * a.Ck + 2.0 * a.Cv));
         qkv_prepare(E.c.stream, a); E.c.cnt.kernels += taps > 1 ? 2 : 1;
+        E.toc();
         WindowAttnArgs w{};
         w.q = E.qbuf; w.kv = kv; w.slopes = slopes; w.scale = scale; w.window = window;
         w.gate = g_off >= 0 ? E.proj + g_off : nullptr; w.gate_ld = in.N; w.out = E.inner; w.H = H; w.rb = v.rb;
+        E.tic("window attention", 2.0 * E.prof_pairs(window) * H * (D + Dv), 4.0 * (T * (double)H * (D + Dv) + E.prof_unique(window) * G * (D + Dv)));
         window_attn(E.c.stream, w); E.c.cnt.kernels++;
+        E.toc();
         E.gemm(AEPI_STORE, E.inner, H * Dv, out, v.y, E.W, T);
     }
 };
@@ -559,6 +734,7 @@ SeqEngine* make_layered_engine(Ctx& ctx, const Json& cfg, const WeightTable& wt,
     const size_t T = e.Tmax;
     e.x = ctx.alloc<float>(T * e.W); e.y = ctx.alloc<float>(T * e.W);
     e.proj = ctx.alloc<float>(T * proj_cols); e.inner = ctx.alloc<float>(T * inner_cols); e.qbuf = ctx.alloc<float>(T * q_cols);
+    if (!e.fp32) { gemm_tc_init(); ctx.split_buf(T * (size_t)std::max({e.W, proj_cols, inner_cols})); }
     e.hn = ctx.alloc<float>((size_t)e.Rmax * e.W); e.logits = ctx.alloc<float>((size_t)e.Rmax * e.V);
     e.meta_ints = 4 * T + (e.slots + 1) + 2 * e.slots + (T + e.slots);
     e.d_meta = ctx.alloc<int>(e.meta_ints);

@@ -10,6 +10,7 @@
 #pragma once
 #include <cstddef>
 #include <cstdint>
+#include <string>
 #include <vector>
 
 #include "../../include/aha_b200.h"
@@ -59,8 +60,10 @@ class SeqEngine {
     virtual size_t read_trace(int layer, float* out, size_t cap) = 0;
     virtual uint64_t weight_bytes() const = 0;
     virtual uint64_t kv_bytes_per_token() const = 0;
-    // device time of `iters` runs of one kernel family on the engine's own buffers, for roofline tables: which = "gemm_up" | "attn" | "scan" | ...
-    virtual void bench(const char* which, int tokens, int ctx, int iters, double* avg_ms, uint64_t* bytes, uint64_t* flops) = 0;
+    // Device-timed steps on synthetic tokens (n_seqs sequences x tokens_per_seq tokens at context ctx) -> JSON: ms per step (CUDA events around
+    // `iters` whole steps, scheduler and host copies included) and, from separate runs with events around every launch family, the time,
+    // algorithmic FLOPs and bytes of each family summed over the layers.  Frees every slot.
+    virtual std::string profile(int n_seqs, int tokens_per_seq, int ctx, int warmup, int iters) = 0;
 };
 
 // config: the checkpoint's config.json (a "layers" list); throws on anything it does not know

@@ -286,6 +286,12 @@ class B200Model:
         self._check(self._lib.aha_b200_seq_info(self._h, slot, C.byref(pos), C.byref(free), C.byref(ns)))
         return {"position": pos.value, "free_tokens": free.value, "max_seqs": ns.value}
 
+    def seq_profile(self, n_seqs, tokens_per_seq, ctx, warmup=3, iters=10):
+        """Device-timed engine steps on synthetic tokens -> dict (see aha_b200_seq_profile)."""
+        buf = C.create_string_buffer(1 << 16)
+        self._check(self._lib.aha_b200_seq_profile(self._h, n_seqs, tokens_per_seq, ctx, warmup, iters, buf, len(buf)))
+        return json.loads(buf.value.decode())
+
     def feed(self, entries):
         """One engine step.  entries: [(slot, token ids, wanted entry-local indices)], any mix of prompt portions and single tokens.
         Returns the logits of the wanted positions in entry order, float32 [rows, vocab]."""

@@ -83,7 +83,7 @@ QWEN3_ASR = {
 
 
 def get_config(kind, preset):
-    return copy.deepcopy({"qwen3": QWEN3, "qwen3vl": QWEN3VL, "qwen3_asr": QWEN3_ASR}[kind][preset])
+    return copy.deepcopy({"qwen3": QWEN3, "qwen3vl": QWEN3VL, "qwen3_asr": QWEN3_ASR, "malasun": MALASUN}[kind][preset])
 
 
 # ----------------------------------------------------------------------------- weights
@@ -142,8 +142,8 @@ def _text_layers(g, p, tc):
     g.gain(p + "norm.weight", H)
 
 
-def make_qwen3(cfg, seed=0):
-    g = _Gen(seed)
+def make_qwen3(cfg, seed=0, fast=False):
+    g = _Gen(seed, fast=fast)
     _text_layers(g, "model.", cfg)
     if not cfg.get("tie_word_embeddings", False):
         g.mat("lm_head.weight", cfg["vocab_size"], cfg["hidden_size"])
@@ -209,8 +209,128 @@ def make_qwen3_asr(cfg, seed=0):
     return g.w
 
 
+# ----------------------------------------------------------------------------- Malasun (layered engine)
+def malasun_config(layers, width=64, vocab=96, eps=1e-5):
+    """config.json of a Malasun model.  layers: list of dicts, each
+         {"type": "hgrn2", "heads", "dim", "vdim", "ff": None | int}
+         {"type": "attention", "heads", "kv_heads", "dim", "vdim", "window": None | int, "conv": None | taps, "scale": float,
+          "kv_from": None | layer index, "ff": None | int}"""
+    out = []
+    for ly in layers:
+        if ly["type"] == "hgrn2":
+            mx = {"heads": ly["heads"], "dim": ly["dim"], "vdim": ly["vdim"]}
+        else:
+            mx = {"heads": ly["heads"], "kv_heads": ly["kv_heads"], "dim": ly["dim"], "vdim": ly["vdim"],
+                  "scale": ly.get("scale", float(ly["dim"]) ** -0.5)}
+            if ly.get("window"):
+                mx["mask"] = {"size": ly["window"]}
+            if ly.get("conv"):
+                mx["conv"] = ly["conv"]
+            if ly.get("kv_from") is not None:
+                mx["kv_from"] = ly["kv_from"]
+        out.append({"type": ly["type"], "mixer": mx, "mlp": {"kind": "dense", "ff": ly["ff"]} if ly.get("ff") else None})
+    return {"architecture": "Malasun", "layers": out, "norm": {"eps": eps}, "vocab": vocab, "width": width}
+
+
+MALASUN = {
+    # every branch once, with sizes that differ from one another: attention first, a feed-forward on a recurrent layer, two kv heads,
+    # dim != vdim, a shared cache read through a narrower window, an attention layer without window / convolution
+    "tiny": malasun_config([
+        {"type": "attention", "heads": 4, "kv_heads": 2, "dim": 16, "vdim": 24, "window": 40, "conv": 3, "ff": 80},
+        {"type": "hgrn2", "heads": 3, "dim": 16, "vdim": 8, "ff": 48},
+        {"type": "attention", "heads": 4, "kv_heads": 2, "dim": 16, "vdim": 24, "window": 17, "conv": 2, "kv_from": 0, "ff": None},
+        {"type": "hgrn2", "heads": 2, "dim": 24, "vdim": 40, "ff": None},
+        {"type": "attention", "heads": 2, "kv_heads": 2, "dim": 32, "vdim": 16, "window": None, "conv": None, "ff": 64},
+    ], width=72, vocab=101),
+}
+
+
+def malasun_shape(width, n_layers, heads, kv_heads, head_dim, window, ff, rec_heads, rec_dim, vocab=32000, taps=4, share_every=2):
+    """A layer list of the sizes a served model would have: recurrent and attention layers alternate, every `share_every`-th attention
+    layer reads the cache of the attention layer before it."""
+    layers, last_kv, n_att = [], None, 0
+    for i in range(n_layers):
+        if i % 2 == 0:
+            layers.append({"type": "hgrn2", "heads": rec_heads, "dim": rec_dim, "vdim": rec_dim, "ff": None})
+        else:
+            share = last_kv is not None and share_every and n_att % share_every == share_every - 1
+            layers.append({"type": "attention", "heads": heads, "kv_heads": kv_heads, "dim": head_dim, "vdim": head_dim, "window": window,
+                           "conv": taps, "kv_from": last_kv if share else None, "ff": ff})
+            if not share:
+                last_kv = i
+            n_att += 1
+    return malasun_config(layers, width=width, vocab=vocab, eps=1e-6)
+
+
+def _bf16_round(a):
+    from ._lib import to_bf16
+    a = np.asarray(a, np.float32)
+    return to_bf16(a).reshape(a.shape)
+
+
+def bf16_to_f32(a):
+    """Values of a `_lib.BF16`-tagged array as float32."""
+    return (np.asarray(a).view(np.ndarray).astype(np.uint32) << 16).view(np.float32)
+
+
+def make_malasun(cfg, seed=0, fast=False):
+    """Random weights under the checkpoint's tensor names, all bfloat16 (`_lib.BF16`-tagged bit patterns)."""
+    rng = np.random.default_rng(seed)
+    w = {}
+
+    def rnd(*shape, std=1.0):
+        if fast:
+            a = rng.random(int(np.prod(shape)), dtype=np.float32)
+            a -= np.float32(0.5)
+            a *= np.float32(std * 3.4641016)
+        else:
+            a = rng.standard_normal(int(np.prod(shape)), dtype=np.float32) * np.float32(std)
+        return a.reshape(shape)
+
+    def put(name, a):
+        w[name] = _bf16_round(a)
+
+    def lin(name, out_f, in_f, gain=1.0):
+        put(name, rnd(out_f, in_f, std=gain / np.sqrt(in_f)))
+
+    W, V = cfg["width"], cfg["vocab"]
+    put("embed", rnd(V, W))
+    lin("head", V, W)
+    put("final.norm", np.float32(1.0 + 0.2 * rng.standard_normal()))
+    for i, ly in enumerate(cfg["layers"]):
+        p, mx = "l%d." % i, ly["mixer"]
+        put(p + "norm1", np.float32(1.0 + 0.2 * rng.standard_normal()))
+        if ly["type"] == "hgrn2":
+            H, D, Dv = mx["heads"], mx["dim"], mx["vdim"]
+            lin(p + "mix.q", H * D, W); lin(p + "mix.f", H * D, W, 2.0); lin(p + "mix.v", H * Dv, W)
+            put(p + "mix.f.b", rnd(H * D, std=1.0))
+            put(p + "mix.lower", 1.0 / (1.0 + np.exp(-rnd(H * D, std=1.5))))
+            put(p + "mix.norm", 1.0 + 0.2 * rnd(Dv))
+            lin(p + "mix.o", W, H * Dv)
+        else:
+            H, G, D, Dv = mx["heads"], mx["kv_heads"], mx["dim"], mx["vdim"]
+            own = "kv_from" not in mx
+            parts = [("q", H * D)] + ([("k", G * D), ("v", G * Dv)] if own else [])
+            for nm, n in parts:
+                lin(p + "mix." + nm, n, W)
+                put(p + "mix." + nm + ".b", rnd(n, std=0.3))
+                if "conv" in mx:
+                    put(p + "mix." + nm + ".conv", rnd(n, mx["conv"], std=0.6))
+            put(p + "mix.q.norm", 1.0 + 0.3 * rnd(H * D))
+            if own:
+                put(p + "mix.k.norm", 1.0 + 0.3 * rnd(G * D))
+            lin(p + "mix.g", H * Dv, W)
+            lin(p + "mix.o", W, H * Dv)
+        if ly.get("mlp"):
+            ff = ly["mlp"]["ff"]
+            put(p + "norm2", np.float32(1.0 + 0.2 * rng.standard_normal()))
+            lin(p + "mlp.up", ff, W); lin(p + "mlp.down", W, ff)
+            put(p + "mlp.act", rnd(2, std=0.7))
+    return w
+
+
 def make_weights(kind, cfg, seed=0):
-    return {"qwen3": make_qwen3, "qwen3vl": make_qwen3vl, "qwen3_asr": make_qwen3_asr}[kind](cfg, seed)
+    return {"qwen3": make_qwen3, "qwen3vl": make_qwen3vl, "qwen3_asr": make_qwen3_asr, "malasun": make_malasun}[kind](cfg, seed)
 
 
 # ----------------------------------------------------------------------------- synthetic inputs

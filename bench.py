@@ -357,6 +357,94 @@ def extra_records(m, wl, synth, r):
             r["batch"] = {"error": f"{type(e).__name__}: {e}"[:300]}
 
 
+# ------------------------------------------------------------------------------------------------- --arch malasun
+# width, layers (recurrent and attention layers alternate), attention heads / kv heads / head size, window, ff, recurrent heads x size, vocab
+MALASUN_SIZES = {
+    "s": dict(width=1024, n_layers=8, heads=8, kv_heads=2, head_dim=128, window=1024, ff=4096, rec_heads=8, rec_dim=64, vocab=32000),
+    "m": dict(width=2048, n_layers=12, heads=16, kv_heads=4, head_dim=128, window=1024, ff=8192, rec_heads=16, rec_dim=128, vocab=32000),
+    "l": dict(width=4096, n_layers=16, heads=32, kv_heads=8, head_dim=128, window=2048, ff=12288, rec_heads=32, rec_dim=128, vocab=32000),
+}
+
+
+def bench_malasun(args):
+    """Prefill (one 2048-token prompt portion) and decode (1 and 8 sequences at context 2048) of a Malasun model with random weights, timed on
+    the device through the engine's own step, with the time of every kernel family against its roofline; beside it Qwen3 of the same width,
+    head layout and feed-forward size with as many layers as the Malasun model has attention layers."""
+    from aha_b200 import B200Model, synth
+    hbm, hbm_src = measured_peaks()
+    try:
+        tf = float(json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))["bf16_tflops"])
+    except Exception:
+        tf = 1590.0
+    K, W = max(args.steps if args.steps != 128 else 16, 4), max(args.warmup, 3)
+    out = {"metric": "Malasun prefill / decode tokens/s beside Qwen3 at equal size", "unit": UNIT, "data": "synthetic", "dtype": "bf16 weights, fp32 accumulate",
+           "peaks": {"hbm_gbs": hbm, "bf16_tflops": tf, "source": hbm_src}, "prompt_tokens": 2048, "decode_ctx": 2048, "sizes": {}}
+    sampler = ClockSampler(0)
+    sampler.start()
+    for name in args.sizes.split(","):
+        sz = MALASUN_SIZES[name]
+        cfg = synth.malasun_shape(**sz)
+        log(f"[malasun {name}] weights ...")
+        w = synth.make_malasun(cfg, 0, fast=True)
+        m = B200Model("malasun", cfg, w, max_ctx=8 * 4096, max_prefill=2048, max_seqs=8)
+        del w
+        rec = {"config": sz, "weight_bytes": m.stats()["weight_bytes"]}
+        for label, (ns, tps, ctx) in {"prefill_2048": (1, 2048, 0), "decode_b1_ctx2048": (1, 1, 2048), "decode_b8_ctx2048": (8, 1, 2048)}.items():
+            pr = m.seq_profile(ns, tps, ctx, W, K)
+            fam = {}
+            for k, v in pr["families"].items():
+                t = v["ms"] * 1e-3
+                roof = max(v["flops"] / (tf * 1e12), v["bytes"] / (hbm * 1e9))
+                fam[k] = {"ms": round(v["ms"], 4), "launches": v["launches"], "roofline_ms": round(roof * 1e3, 4), "of_roofline": round(roof / t, 4) if t > 0 else None,
+                          "bound": "tensor" if v["flops"] / (tf * 1e12) > v["bytes"] / (hbm * 1e9) else "HBM"}
+            rec[label] = {"tokens_per_s": round(pr["tokens_per_step"] / (pr["ms_per_step"] * 1e-3), 1), "ms_per_step": round(pr["ms_per_step"], 4),
+                          "kernels_per_step": pr["kernels_per_step"], "graph_launches_per_step": pr["graph_launches_per_step"], "families": fam}
+            log(f"[malasun {name}] {label}: {rec[label]['tokens_per_s']} tok/s")
+        m.close()
+        # Qwen3 at equal size
+        n_att = sum(1 for ly in cfg["layers"] if ly["type"] == "attention")
+        qc = dict(synth.get_config("qwen3", "tiny"))
+        qc.update(hidden_size=sz["width"], intermediate_size=sz["ff"], num_hidden_layers=n_att, num_attention_heads=sz["heads"], num_key_value_heads=sz["kv_heads"],
+                  head_dim=128, vocab_size=sz["vocab"], tie_word_embeddings=False)
+        log(f"[qwen3 {name}] weights ...")
+        qw = synth.make_qwen3(qc, 0, fast=True)
+        q = B200Model("qwen3", qc, qw, eos_ids=[qc.get("eos_token_id", 0)], max_ctx=4096, max_prefill=2048)
+        del qw
+        ids = synth.synth_text_ids(2048, sz["vocab"], 1)
+        import torch
+        stream = torch.cuda.ExternalStream(q.stream_ptr())
+        for _ in range(W):
+            q.clear_cache(); q.forward_initial(ids, 0, want_logits=False)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ms = []
+        for _ in range(max(3, K // 2)):
+            q.clear_cache()
+            e0.record(stream); q.forward_initial(ids, 0, want_logits=False); e1.record(stream); e1.synchronize()
+            ms.append(e0.elapsed_time(e1))
+        qrec = {"layers": n_att, "weight_bytes": q.stats()["weight_bytes"], "prefill_2048": {"tokens_per_s": round(2048 / (statistics.median(ms) * 1e-3), 1), "ms": round(statistics.median(ms), 4)}}
+        q.decode_steps(1, 2048, W, want_tokens=False)
+        _, dms = q.decode_steps(1, 2048, 4 * K, want_tokens=False, timed=True)
+        qrec["decode_b1_ctx2048"] = {"tokens_per_s": round(4 * K / (dms * 1e-3), 1), "ms_per_step": round(dms / (4 * K), 4)}
+        # 8 requests in lockstep (its batch decoder): prompts of 2040 tokens, 9 tokens each
+        t0 = time.time()
+        q.clear_cache()
+        outs = q.generate_batch([dict(input_ids=synth.synth_text_ids(2040, sz["vocab"], 10 + i), max_tokens=2) for i in range(8)])
+        t_short = time.time() - t0
+        t0 = time.time()
+        outs = q.generate_batch([dict(input_ids=synth.synth_text_ids(2040, sz["vocab"], 10 + i), max_tokens=2 + 4 * K) for i in range(8)])
+        t_long = time.time() - t0
+        steps = 4 * K
+        qrec["decode_b8_ctx2048"] = {"tokens_per_s": round(8 * steps / max(t_long - t_short, 1e-9), 1), "ms_per_step": round((t_long - t_short) / steps * 1e3, 4),
+                                     "timing": "wall clock of two generate_batch calls that differ by the decode steps"}
+        for k in ("prefill_2048", "decode_b1_ctx2048", "decode_b8_ctx2048"):
+            log(f"[qwen3 {name}] {k}: {qrec[k]['tokens_per_s']} tok/s")
+        q.close()
+        rec["qwen3_equal_size"] = qrec
+        out["sizes"][name] = rec
+    out["clocks"] = sampler.stop()
+    emit(out)
+
+
 def main():
     global _REAL_STDOUT
     sys.stdout.flush()
@@ -371,7 +459,12 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-tp", action="store_true", help="N > 1: skip the tensor-parallel (strong scaling) arm")
     ap.add_argument("--decode-impl", type=int, default=int(os.environ.get("AHA_DECODE_IMPL", "0")))
+    ap.add_argument("--arch", default="", help="'malasun': throughput of the layered engine's Malasun design at model-like sizes beside Qwen3 at equal "
+                                               "width / depth (a separate report; the default workload and its JSON line are unchanged)")
+    ap.add_argument("--sizes", default="s,m", help="--arch malasun: which of the sizes s, m, l to run")
     args = ap.parse_args()
+    if args.arch == "malasun":
+        return bench_malasun(args)
     K, W = args.steps, max(args.warmup, 3)
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

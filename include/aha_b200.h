@@ -316,6 +316,10 @@ typedef struct aha_feed_entry {
 int aha_b200_seq_open(aha_model* m, int32_t* slot_out);
 int aha_b200_seq_close(aha_model* m, int32_t slot);
 int aha_b200_seq_feed(aha_model* m, const aha_feed_entry* entries, size_t n, float* logits_out, size_t cap_rows);
+/* Timing of the engine's own step on synthetic tokens: n_seqs sequences each feeding tokens_per_seq tokens at context ctx (prefill: 1 x 2048 at 0;
+ * decode: 8 x 1 at 4096).  json_out: {"ms_per_step" (CUDA events around `iters` whole steps), "kernels_per_step", "families": {name: {"ms", "flops",
+ * "bytes", "launches"}}} -- the families' device times come from separate runs with events around every launch.  Frees every slot. */
+int aha_b200_seq_profile(aha_model* m, int32_t n_seqs, int32_t tokens_per_seq, int32_t ctx, int32_t warmup, int32_t iters, char* json_out, size_t cap);
 /* position of a slot (slot < 0: skipped), unmapped KV capacity in tokens, number of slots; any pointer may be NULL */
 int aha_b200_seq_info(aha_model* m, int32_t slot, int64_t* position_out, int64_t* free_tokens_out, int32_t* max_seqs_out);
 

@@ -4,8 +4,8 @@ A Malasun model is a list of layers read from config["layers"]; every layer is  
 feed-forward,  x += norm2(ff(x))  -- the scalar-gain RMS norms sit on the sublayer OUTPUTS, the sublayers read x itself.
 Two mixers exist:
 
-  hgrn2      gated linear recurrence per head:  S_t = diag(f_t) S_{t-1} + (1 - f_t) v_t^T,  o_t = S_t^T q_t,
-             f_t = l + (1 - l) sigmoid(W_f h + b_f),  q_t = silu(W_q h)
+  hgrn2      gated linear recurrence per head with a [dim, vdim] state:  S[i, j] <- f[i] S[i, j] + (1 - f[i]) v[j],
+             o[j] = sum_i S[i, j] q[i],  with the gate f = lo + (1 - lo) sigmoid(f_raw) and q = silu(q_raw)
   attention  grouped-query softmax attention over a sliding window with a linear distance penalty slope_h (i - j),
              biased q/k/v projections, a short causal convolution on q, k and v, RMS norm of q and k over the whole
              projection, a sigmoid output gate, and optionally the keys / values of an earlier layer ("kv_from")
@@ -24,7 +24,7 @@ def rms_unit(x, eps):
 
 def scalar_norm(x, g, eps):
     """RMS norm whose gain is ONE number for all coordinates."""
-    return rms_unit(x, eps) * F(g)
+    return rms_unit(x, eps) * F(np.asarray(g).reshape(-1)[0])
 
 
 def sigmoid(z):
@@ -40,7 +40,7 @@ def silu(z):
 
 
 def xielu(z, p, q):
-    """z > 0: softplus(p) z^2 + z/2;  z <= 0: (1/2 + softplus(q)) (exp(z) - 1 - z) + z/2."""
+    """a_p z^2 + z/2 for positive z, a_n (e^z - 1 - z) + z/2 otherwise; a_p = softplus(p), a_n = 1/2 + softplus(q)."""
     ap, aq = softplus(F(p)), 0.5 + softplus(F(q))
     pos = ap * z * z + 0.5 * z
     neg = aq * (np.expm1(np.minimum(z, 0.0)) - z) + 0.5 * z
