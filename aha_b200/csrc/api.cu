@@ -578,6 +578,7 @@ int aha_b200_create(const char* kind, const char* config_json, const aha_tensor_
             so.fp32 = o.reserved[1] == 1;
             so.use_graph = o.use_graph != 0;
             so.gemm_impl = o.gemm_impl;
+            so.seq_impl = o.reserved[0] == 1 ? 1 : 0;     // attn_impl 1: the plain sequence kernels
             m->seq.reset(make_layered_engine(m->ctx, root, wt, so));
         } else {
             throw std::runtime_error("unknown model kind '" + k + "' (expected qwen3 | qwen3vl | qwen3_asr | malasun)");

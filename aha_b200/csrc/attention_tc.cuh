@@ -99,6 +99,12 @@ struct FlashTcArgs {
     __half *out_hi, *out_lo;   // when set: the output goes out as fp16 hi + lo halves (operand format of the next GEMM) instead of fp32
     int Sq, Skv, q0, groups;
     float scaling;
+    // WIN kernels only: a sliding window (query i sees keys j with 0 <= i - j < window; 0 = all earlier keys), a distance penalty
+    // slopes[head] * (i - j) taken off the scaled score, and a sigmoid output gate read from gate[(q0 + i) * gate_tok_stride + head * HD + c]
+    int window = 0;
+    const float* slopes = nullptr;
+    const float* gate = nullptr;
+    size_t gate_tok_stride = 0;
 };
 
 __device__ __forceinline__ float ex2_approx(float x) {   // 2^x on the MUFU, flush-to-zero (inputs here are <= 0; -inf -> 0)
@@ -116,7 +122,7 @@ __device__ __forceinline__ void pack8_split(const float* p, uint4& hi, uint4& lo
     split2(p[6], p[7], hi.w, lo.w);
 }
 
-template <int HD, bool CAUSAL>
+template <int HD, bool CAUSAL, bool WIN = false>
 __global__ void __launch_bounds__(kFaThreads, HD == 64 ? 2 : 1) flash_attn_tc_kernel(const __grid_constant__ CUtensorMap tm_qh, const __grid_constant__ CUtensorMap tm_ql,
                                                                      const __grid_constant__ CUtensorMap tm_kh, const __grid_constant__ CUtensorMap tm_kl,
                                                                      const __grid_constant__ CUtensorMap tm_vh, const __grid_constant__ CUtensorMap tm_vl, FlashTcArgs a) {
@@ -139,7 +145,9 @@ __global__ void __launch_bounds__(kFaThreads, HD == 64 ? 2 : 1) flash_attn_tc_ke
     const int causal_shift = a.Skv - a.Sq;
     int kv_end = a.Skv;
     if (CAUSAL) kv_end = min(a.Skv, qt0 + BQ + causal_shift);
-    const int ntiles = (kv_end + BKV - 1) / BKV;
+    // WIN: the KV tiles before the window of the block's first query are never visited; tile t of the loops below is KV tile t_begin + t
+    const int t_begin = (WIN && a.window > 0) ? max(0, qt0 + causal_shift - a.window + 1) / BKV : 0;
+    const int ntiles = (kv_end + BKV - 1) / BKV - t_begin;
 
     if (tid == 0) {
         mbar_init(bar_q, 1); mbar_init(bar_k, 1); mbar_init(bar_v, 1); mbar_init(&bar_s[0], 1); mbar_init(&bar_s[1], 1); mbar_init(bar_o, 1); mbar_init(bar_p, BQ);
@@ -163,8 +171,8 @@ __global__ void __launch_bounds__(kFaThreads, HD == 64 ? 2 : 1) flash_attn_tc_ke
                 mbar_expect_tx(bar_k, 2 * kKBytes);
 #pragma unroll
                 for (int kb = 0; kb < KB; ++kb) {
-                    tma_load_2d(Kh + kb * kKBlk, &tm_kh, kb * 64, krow + t * BKV, bar_k);
-                    tma_load_2d(Kl + kb * kKBlk, &tm_kl, kb * 64, krow + t * BKV, bar_k);
+                    tma_load_2d(Kh + kb * kKBlk, &tm_kh, kb * 64, krow + (t_begin + t) * BKV, bar_k);
+                    tma_load_2d(Kl + kb * kKBlk, &tm_kl, kb * 64, krow + (t_begin + t) * BKV, bar_k);
                 }
             };
             mbar_expect_tx(bar_q, 2 * kQBytes);
@@ -175,8 +183,8 @@ __global__ void __launch_bounds__(kFaThreads, HD == 64 ? 2 : 1) flash_attn_tc_ke
             }
             load_k(0);
             mbar_expect_tx(bar_v, 2 * kVBytes);
-            tma_load_2d(Vh, &tm_vh, 0, vrow, bar_v);
-            tma_load_2d(Vl, &tm_vl, 0, vrow, bar_v);
+            tma_load_2d(Vh, &tm_vh, t_begin * BKV, vrow, bar_v);
+            tma_load_2d(Vl, &tm_vl, t_begin * BKV, vrow, bar_v);
             const uint32_t idesc = umma_idesc_f16(BQ, 64), idesc_pv = umma_idesc_f16(BQ, HD);
             const uint64_t d_qh = umma_desc_sw128(Qh), d_ql = umma_desc_sw128(Ql), d_kh = umma_desc_sw128(Kh), d_kl = umma_desc_sw128(Kl);
             const uint64_t d_vh = umma_desc_sw128(Vh), d_vl = umma_desc_sw128(Vl), d_ph = umma_desc_sw128(Ph), d_pl = umma_desc_sw128(Pl);
@@ -220,8 +228,8 @@ __global__ void __launch_bounds__(kFaThreads, HD == 64 ? 2 : 1) flash_attn_tc_ke
                 if (t >= 1) {
                     mbar_wait(bar_o, (uint32_t)((t - 1) & 1));    // PV(t - 1) done: the V tile is free, fetch V(t)
                     mbar_expect_tx(bar_v, 2 * kVBytes);
-                    tma_load_2d(Vh, &tm_vh, t * BKV, vrow, bar_v);
-                    tma_load_2d(Vl, &tm_vl, t * BKV, vrow, bar_v);
+                    tma_load_2d(Vh, &tm_vh, (t_begin + t) * BKV, vrow, bar_v);
+                    tma_load_2d(Vl, &tm_vl, (t_begin + t) * BKV, vrow, bar_v);
                 }
             }
             issue_pv(ntiles - 1);
@@ -236,10 +244,11 @@ __global__ void __launch_bounds__(kFaThreads, HD == 64 ? 2 : 1) flash_attn_tc_ke
         for (int c = 0; c < HD; ++c) o[c] = 0.f;
         float m = -INFINITY, l = 0.f;                            // m in the log2 domain: exp(x) = 2^(x * log2 e)
         const float scale_log2 = a.scaling * 1.4426950408889634f;
+        const float pen = (WIN && a.slopes) ? a.slopes[head] * 1.4426950408889634f : 0.f;   // the distance penalty in the log2 domain
         uint8_t* prow_h = Ph + (size_t)row * 128;
         uint8_t* prow_l = Pl + (size_t)row * 128;
         for (int t = 0; t < ntiles; ++t) {
-            const int kt0 = t * BKV;
+            const int kt0 = (t_begin + t) * BKV;
             mbar_wait(&bar_s[t & 1], (uint32_t)((t >> 1) & 1));
             tc_fence_after();
             float s[BKV];
@@ -256,6 +265,27 @@ __global__ void __launch_bounds__(kFaThreads, HD == 64 ? 2 : 1) flash_attn_tc_ke
             // and max subtraction in ONE fma feeding ex2.approx, and the rescale of O skipped while no row of the warp moved its max.
             const bool mask_tile = (kt0 + BKV > a.Skv) || (CAUSAL && kt0 + BKV - 1 > qt0 + (int)(warp * 32) + causal_shift);
             float rmax = -INFINITY;
+            float mn, mu, alpha, rs = 0.f;
+            if (WIN) {
+                // the penalty differs from key to key, so the scores are brought to the log2 domain (scale, penalty) BEFORE the max; a tile
+                // that lies inside the window of every row of the warp needs no mask
+                const int wq = qt0 + (int)(warp * 32) + causal_shift;       // key index of the warp's first query
+                const bool inside = !mask_tile && (a.window <= 0 || kt0 >= wq + 31 - a.window + 1);
+                const int qk = qi + causal_shift;
+#pragma unroll
+                for (int c = 0; c < BKV; ++c) {
+                    const int dist = qk - (kt0 + c);
+                    float x = fmaf(s[c], scale_log2, -pen * (float)dist);
+                    if (!inside && (dist < 0 || kt0 + c >= a.Skv || (a.window > 0 && dist >= a.window))) x = -INFINITY;
+                    s[c] = x;
+                    rmax = fmaxf(rmax, x);
+                }
+                mn = fmaxf(m, rmax);
+                mu = (mn == -INFINITY) ? 0.f : mn;
+                alpha = ex2_approx(m - mu);
+#pragma unroll
+                for (int c = 0; c < BKV; ++c) { s[c] = ex2_approx(s[c] - mu); rs += s[c]; }
+            } else {
             if (mask_tile) {
 #pragma unroll
                 for (int c = 0; c < BKV; ++c) {
@@ -267,12 +297,12 @@ __global__ void __launch_bounds__(kFaThreads, HD == 64 ? 2 : 1) flash_attn_tc_ke
 #pragma unroll
                 for (int c = 0; c < BKV; ++c) rmax = fmaxf(rmax, s[c]);
             }
-            const float mn = fmaxf(m, rmax * scale_log2);
-            const float mu = (mn == -INFINITY) ? 0.f : mn;
-            const float alpha = ex2_approx(m - mu);
-            float rs = 0.f;
+            mn = fmaxf(m, rmax * scale_log2);
+            mu = (mn == -INFINITY) ? 0.f : mn;
+            alpha = ex2_approx(m - mu);
 #pragma unroll
             for (int c = 0; c < BKV; ++c) { s[c] = ex2_approx(fmaf(s[c], scale_log2, -mu)); rs += s[c]; }
+            }
             l = l * alpha + rs;
             m = mn;
             if (t >= 1) {   // PV(t - 1) ran under the arithmetic above; it also has to be done before P(t) may overwrite P(t - 1)
@@ -320,6 +350,14 @@ __global__ void __launch_bounds__(kFaThreads, HD == 64 ? 2 : 1) flash_attn_tc_ke
         if (qi < a.Sq) {
             const float inv = 1.0f / l;
             const size_t off = (size_t)(a.q0 + qi) * a.o_tok_stride + (size_t)head * a.o_head_stride;
+            if (WIN && a.gate) {
+                const float* gr = a.gate + (size_t)(a.q0 + qi) * a.gate_tok_stride + (size_t)head * HD;
+#pragma unroll
+                for (int c = 0; c < HD; c += 4) {
+                    const float4 g4 = *reinterpret_cast<const float4*>(gr + c);
+                    o[c] *= sigmoid_f(g4.x); o[c + 1] *= sigmoid_f(g4.y); o[c + 2] *= sigmoid_f(g4.z); o[c + 3] *= sigmoid_f(g4.w);
+                }
+            }
             if (a.out_hi) {
 #pragma unroll
                 for (int c = 0; c < HD; c += 8) {
@@ -360,10 +398,18 @@ inline void flash_attn_tc_init() {
     AHA_CUDA_CHECK(cudaFuncSetAttribute(flash_attn_tc_kernel<64, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)flash_tc_smem_bytes<64>()));
     AHA_CUDA_CHECK(cudaFuncSetAttribute(flash_attn_tc_kernel<128, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)flash_tc_smem_bytes<128>()));
     AHA_CUDA_CHECK(cudaFuncSetAttribute(flash_attn_tc_kernel<128, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)flash_tc_smem_bytes<128>()));
+    AHA_CUDA_CHECK(cudaFuncSetAttribute(flash_attn_tc_kernel<64, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)flash_tc_smem_bytes<64>()));
+    AHA_CUDA_CHECK(cudaFuncSetAttribute(flash_attn_tc_kernel<128, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)flash_tc_smem_bytes<128>()));
 }
+struct FlashWindow {        // what the WIN kernels add to causal attention; window 0, no slopes and no gate is plain causal attention
+    int window = 0;
+    const float* slopes = nullptr;
+    const float* gate = nullptr;
+    size_t gate_tok_stride = 0;
+};
 // head_dim 64 (ViT, audio encoder: 2 CTAs per SM) and 128 (LLM prefill, causal, GQA, paged KV: 1 CTA per SM).  `ws`: at least flash_tc_ws_halfs<HD>() halfs.
 template <int HD>
-inline void flash_attn_tc(cudaStream_t st, const FlashArgs& a, int nheads, bool causal, __half* ws) {
+inline void flash_attn_tc(cudaStream_t st, const FlashArgs& a, int nheads, bool causal, __half* ws, const FlashWindow* win = nullptr) {
     if (a.Sq == 0) return;
     const int nkv = nheads / a.groups, pad = flash_tc_skv_pad(a.Skv);
     SplitTcArgs sp;
@@ -372,6 +418,7 @@ inline void flash_attn_tc(cudaStream_t st, const FlashArgs& a, int nheads, bool 
     sp.q_hi = ws; sp.q_lo = ws + nq; sp.k_hi = ws + 2 * nq; sp.k_lo = sp.k_hi + nk; sp.vt_hi = sp.k_lo + nk; sp.vt_lo = sp.vt_hi + nv;
     const unsigned blocks = (unsigned)std::min<size_t>(std::max<size_t>(ceil_div((int)std::max((size_t)nheads * a.Sq, (size_t)nkv * a.Skv), 512 / HD), (size_t)nkv * (pad / 64)), 148 * 32);
     split_qkv_tc_kernel<HD><<<dim3(blocks, 3), 128, 0, st>>>(sp);
+    AHA_CUDA_CHECK(cudaGetLastError());
     const CUtensorMap tqh = make_tmap_f16_box(sp.q_hi, (uint64_t)nheads * a.Sq, HD, kFaBQ), tql = make_tmap_f16_box(sp.q_lo, (uint64_t)nheads * a.Sq, HD, kFaBQ);
     const CUtensorMap tkh = make_tmap_f16_box(sp.k_hi, (uint64_t)nkv * a.Skv, HD, kFaBKV), tkl = make_tmap_f16_box(sp.k_lo, (uint64_t)nkv * a.Skv, HD, kFaBKV);
     const CUtensorMap tvh = make_tmap_f16_box(sp.vt_hi, (uint64_t)nkv * HD, (uint64_t)pad, HD), tvl = make_tmap_f16_box(sp.vt_lo, (uint64_t)nkv * HD, (uint64_t)pad, HD);
@@ -380,7 +427,12 @@ inline void flash_attn_tc(cudaStream_t st, const FlashArgs& a, int nheads, bool 
     m.Sq = a.Sq; m.Skv = a.Skv; m.q0 = a.q0; m.groups = a.groups; m.scaling = a.scaling;
     dim3 grid(ceil_div(a.Sq, kFaBQ), nheads);
     const size_t smem = flash_tc_smem_bytes<HD>();
-    if (causal) flash_attn_tc_kernel<HD, true><<<grid, kFaThreads, smem, st>>>(tqh, tql, tkh, tkl, tvh, tvl, m);
+    if (win) {
+        AHA_REQUIRE(causal, "windowed attention is causal");
+        m.window = win->window; m.slopes = win->slopes; m.gate = win->gate; m.gate_tok_stride = win->gate_tok_stride;
+        AHA_CUDA_CHECK(cudaFuncSetAttribute(flash_attn_tc_kernel<HD, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        flash_attn_tc_kernel<HD, true, true><<<grid, kFaThreads, smem, st>>>(tqh, tql, tkh, tkl, tvh, tvl, m);
+    } else if (causal) flash_attn_tc_kernel<HD, true><<<grid, kFaThreads, smem, st>>>(tqh, tql, tkh, tkl, tvh, tvl, m);
     else flash_attn_tc_kernel<HD, false><<<grid, kFaThreads, smem, st>>>(tqh, tql, tkh, tkl, tvh, tvl, m);
     AHA_CUDA_CHECK(cudaGetLastError());
 }

@@ -123,59 +123,99 @@ struct WindowAttnArgs {
     float* out;              // [T, H*Dv]
     int H;
     RaggedBatch rb;
+    int skip_from_n = 0;     // > 0: tokens of entries that bring at least this many tokens are left to another kernel
+    // split launches (decode-sized steps): the visible keys of a token are cut into `nsplit` chunks of `chunk` keys, one block each
+    float* part = nullptr;   // [T][H][nsplit][2 + Dv]: running max, sum of weights, un-normalised weighted values
+    int nsplit = 1, chunk = 0;
 };
 
 constexpr int kWinAttnThreads = 128;
 constexpr int kWinAttnMaxAcc = 4;    // Dv <= 4 * 128
+constexpr int kWinSplitMaxTokens = 32, kWinMaxSplits = 32;
 
+// One block per (token, head[, chunk of keys]).  Scores: a warp takes four keys at a time, its lanes run over the head dimension (one
+// coalesced read of each key row), so a tile of 128 keys costs 8 rounds per warp; softmax over the tile across the block; values: thread
+// c owns output channel c (+ 128, ...) and walks the tile's value rows, which are contiguous across the threads.
+template <bool SPLIT>
 static __global__ void __launch_bounds__(kWinAttnThreads) window_attn_kernel(WindowAttnArgs a) {
     extern __shared__ float sm[];
     const int D = a.kv.D, Dv = a.kv.Dv;
     float* qs = sm;                 // [D]
     float* sc = sm + D;             // [threads]
     float* red = sc + kWinAttnThreads;   // [32]
-    const int t = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
+    const int t = blockIdx.x, h = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = h / (a.H / a.kv.G);
     const int e = a.rb.tok_entry[t], i = a.rb.tok_pos[t], slot = a.rb.ent_slot[e];
+    if (!SPLIT && a.skip_from_n > 0 && a.rb.ent_start[e + 1] - a.rb.ent_start[e] >= a.skip_from_n) return;
     const int* pt = a.rb.page_tables + (size_t)slot * a.rb.max_pages;
     const float slope = a.slopes ? a.slopes[h] : 0.f;
+    int ja = a.window > 0 ? max(0, i - a.window + 1) : 0, jb = i + 1;          // visible keys [ja, jb)
+    float* P = nullptr;
+    if (SPLIT) {
+        ja += blockIdx.z * a.chunk;
+        jb = min(ja + a.chunk, jb);
+        P = a.part + (((size_t)t * a.H + h) * a.nsplit + blockIdx.z) * (size_t)(2 + Dv);
+        if (ja >= jb) { if (tid == 0) { P[0] = -INFINITY; P[1] = 0.f; } return; }
+    }
     for (int d = tid; d < D; d += kWinAttnThreads) qs[d] = a.q[(size_t)t * a.H * D + h * D + d];
     __syncthreads();
-    const int j0 = a.window > 0 ? max(0, i - a.window + 1) : 0;
     float m = -INFINITY, l = 0.f;
     float acc[kWinAttnMaxAcc];
 #pragma unroll
     for (int r = 0; r < kWinAttnMaxAcc; ++r) acc[r] = 0.f;
-    for (int jb = j0; jb <= i; jb += kWinAttnThreads) {
-        const int j = jb + tid;
-        float s = -INFINITY;
-        if (j <= i) {
-            const float* kr = a.kv.k_row(pt[j >> kPageShift], g, j & (kPage - 1));
-            float dot = 0.f;
-            for (int d = 0; d < D; ++d) dot = fmaf(qs[d], kr[d], dot);
-            s = dot * a.scale - slope * (float)(i - j);
+    for (int jt = ja; jt < jb; jt += kWinAttnThreads) {
+        const int nj = min(kWinAttnThreads, jb - jt);
+        for (int k0 = warp * 4; k0 < nj; k0 += 16) {
+            const float* kr[4];
+            float dot[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int j = jt + min(k0 + u, nj - 1);
+                kr[u] = a.kv.k_row(pt[j >> kPageShift], g, j & (kPage - 1));
+            }
+            for (int d = lane; d < D; d += 32) {
+                const float qd = qs[d];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) dot[u] = fmaf(qd, kr[u][d], dot[u]);
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const float v = warp_sum(dot[u]);
+                if (lane == 0 && k0 + u < nj) sc[k0 + u] = v * a.scale - slope * (float)(i - (jt + k0 + u));
+            }
         }
+        __syncthreads();
+        const float s = tid < nj ? sc[tid] : -INFINITY;
         const float m_new = fmaxf(m, block_max(s, red));
-        const float p = j <= i ? expf(s - m_new) : 0.f;
+        const float p = tid < nj ? expf(s - m_new) : 0.f;
         const float corr = expf(m - m_new);          // m = -inf on the first tile: 0
         sc[tid] = p;
         const float psum = block_sum(p, red);          // its barriers publish sc
         l = l * corr + psum;
         m = m_new;
-        const int nj = min(kWinAttnThreads, i - jb + 1);
 #pragma unroll
         for (int r = 0; r < kWinAttnMaxAcc; ++r) {
             const int c = tid + r * kWinAttnThreads;
             if (c < Dv) {
                 float o = acc[r] * corr;
+#pragma unroll 4
                 for (int jj = 0; jj < nj; ++jj) {
-                    const int jk = jb + jj;
+                    const int jk = jt + jj;
                     o = fmaf(sc[jj], a.kv.v_row(pt[jk >> kPageShift], g, jk & (kPage - 1))[c], o);
                 }
                 acc[r] = o;
             }
         }
         __syncthreads();     // sc is rewritten by the next tile
+    }
+    if (SPLIT) {
+        if (tid == 0) { P[0] = m; P[1] = l; }
+#pragma unroll
+        for (int r = 0; r < kWinAttnMaxAcc; ++r) {
+            const int c = tid + r * kWinAttnThreads;
+            if (c < Dv) P[2 + c] = acc[r];
+        }
+        return;
     }
     const float inv = 1.0f / l;
 #pragma unroll
@@ -189,6 +229,24 @@ static __global__ void __launch_bounds__(kWinAttnThreads) window_attn_kernel(Win
     }
 }
 
+// merges the chunks of a (token, head): weights exp(m_s - M) bring every partial sum to the common maximum
+static __global__ void __launch_bounds__(kWinAttnThreads) window_attn_merge_kernel(WindowAttnArgs a) {
+    const int t = blockIdx.x, h = blockIdx.y, Dv = a.kv.Dv;
+    const float* P = a.part + ((size_t)t * a.H + h) * a.nsplit * (size_t)(2 + Dv);
+    float M = -INFINITY;
+    for (int s = 0; s < a.nsplit; ++s) M = fmaxf(M, P[(size_t)s * (2 + Dv)]);
+    float L = 0.f;
+    for (int s = 0; s < a.nsplit; ++s) { const float* ps = P + (size_t)s * (2 + Dv); if (ps[1] > 0.f) L += ps[1] * expf(ps[0] - M); }
+    const float inv = 1.0f / L;
+    for (int c = threadIdx.x; c < Dv; c += kWinAttnThreads) {
+        float o = 0.f;
+        for (int s = 0; s < a.nsplit; ++s) { const float* ps = P + (size_t)s * (2 + Dv); if (ps[1] > 0.f) o = fmaf(ps[2 + c], expf(ps[0] - M), o); }
+        o *= inv;
+        if (a.gate) o *= sigmoid_f(a.gate[(size_t)t * a.gate_ld + h * Dv + c]);
+        a.out[(size_t)t * a.H * Dv + h * Dv + c] = o;
+    }
+}
+
 inline void qkv_prepare(cudaStream_t st, const QkvPrepArgs& a) {
     if (a.rb.T == 0) return;
     AHA_REQUIRE(a.taps <= kConvMaxTaps, "short convolution: more than 16 taps");
@@ -197,12 +255,26 @@ inline void qkv_prepare(cudaStream_t st, const QkvPrepArgs& a) {
     AHA_CUDA_CHECK(cudaGetLastError());
 }
 
-inline void window_attn(cudaStream_t st, const WindowAttnArgs& a) {
-    if (a.rb.T == 0) return;
+inline size_t window_attn_part_floats(int H, int Dv) { return (size_t)kWinSplitMaxTokens * H * kWinMaxSplits * (2 + Dv); }
+
+// kv_span: an upper bound of the keys any token of the step sees (the window, or the longest sequence of the step); `part` != nullptr
+// and a decode-sized step: the keys are cut into chunks, one block each, and merged.  Returns the launches.
+inline int window_attn(cudaStream_t st, WindowAttnArgs a, int kv_span) {
+    if (a.rb.T == 0) return 0;
     AHA_REQUIRE(a.kv.Dv <= kWinAttnMaxAcc * kWinAttnThreads, "window attention: value head size above 512");
     const size_t smem = ((size_t)a.kv.D + kWinAttnThreads + 32) * sizeof(float);
-    window_attn_kernel<<<dim3(a.rb.T, a.H), kWinAttnThreads, smem, st>>>(a);
+    if (a.part && a.rb.T <= kWinSplitMaxTokens && kv_span > kWinAttnThreads) {
+        a.nsplit = std::min(kWinMaxSplits, ceil_div(kv_span, kWinAttnThreads));
+        a.chunk = ceil_div(ceil_div(kv_span, a.nsplit), kWinAttnThreads) * kWinAttnThreads;
+        a.skip_from_n = 0;
+        window_attn_kernel<true><<<dim3(a.rb.T, a.H, a.nsplit), kWinAttnThreads, smem, st>>>(a);
+        window_attn_merge_kernel<<<dim3(a.rb.T, a.H), kWinAttnThreads, 0, st>>>(a);
+        AHA_CUDA_CHECK(cudaGetLastError());
+        return 2;
+    }
+    window_attn_kernel<false><<<dim3(a.rb.T, a.H), kWinAttnThreads, smem, st>>>(a);
     AHA_CUDA_CHECK(cudaGetLastError());
+    return 1;
 }
 
 }  // namespace aha

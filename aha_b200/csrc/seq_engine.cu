@@ -17,6 +17,7 @@
 #include <functional>
 #include <memory>
 
+#include "attention_tc.cuh"
 #include "attention_window.cuh"
 #include "gemm_any.cuh"
 #include "gemm_tc.cuh"
@@ -41,6 +42,7 @@ struct LinearAny {
 
 constexpr int kTcMinRows = 32;    // fewer rows than this run on the CUDA cores (a 128-row tensor-core tile would be mostly padding)
 constexpr int kGraphMaxTokens = 8;   // launches of at most this many tokens (decode steps) are replayed from CUDA graphs
+constexpr int kTcAttnMinTokens = 32; // a prompt portion of at least this many tokens runs its attention on the tcgen05 flash kernel (serving mode, head size 64 / 128)
 
 struct Engine;
 
@@ -50,6 +52,10 @@ struct StepView {
     RaggedBatch rb;
     const float* x;     // [T, width] sublayer input (the residual stream)
     float* y;           // [T, width] sublayer output (before its norm)
+    const int* h_ent_start;   // host copies of rb.ent_start / ent_pos0 / ent_slot
+    const int* h_ent_pos0;
+    const int* h_ent_slot;
+    int span;           // a power of two >= the tokens the longest sequence of the step holds after it (part of a replayed graph's key)
 };
 
 struct Sublayer {
@@ -58,6 +64,7 @@ struct Sublayer {
     virtual int proj_cols() const = 0;     // widest intermediate row this sublayer needs in Engine::proj
     virtual int inner_cols() const = 0;    // ... in Engine::inner
     virtual int q_cols() const { return 0; }
+    virtual size_t attn_part_floats() const { return 0; }     // workspace of the split attention launches
     virtual uint64_t kv_bytes_per_token() const { return 0; }
 };
 
@@ -84,7 +91,7 @@ struct Engine final : SeqEngine {
     std::vector<Seq> seqs;
     // step scratch
     int Tmax = 0, Rmax = 0;
-    float *x = nullptr, *y = nullptr, *proj = nullptr, *inner = nullptr, *qbuf = nullptr, *hn = nullptr, *logits = nullptr;
+    float *x = nullptr, *y = nullptr, *proj = nullptr, *inner = nullptr, *qbuf = nullptr, *hn = nullptr, *logits = nullptr, *attn_part = nullptr;
     int* d_meta = nullptr; int* h_meta = nullptr; size_t meta_ints = 0;
     cudaEvent_t ev_meta = nullptr; bool meta_pending = false;
     // sampler state per slot
@@ -352,6 +359,9 @@ struct Engine final : SeqEngine {
             t += p.cnt;
         }
         ent_start[E] = T;
+        int span = 128;
+        for (int i = 0; i < E; ++i) while (span < ent_pos0[i] + (ent_start[i + 1] - ent_start[i])) span *= 2;
+        cur_span = span;
         const int n_want_rows = nrows;
         for (int i = 0, tt = 0; i < E; ++i) {     // sampled rows come after the wanted ones
             const Piece& p = pieces[i];
@@ -374,7 +384,7 @@ struct Engine final : SeqEngine {
         // ---- device work.  Decode-sized launches are replayed from a CUDA graph keyed by everything the launch arguments depend on.
         const bool graphable = opt.use_graph && !trace && !profiling && T <= kGraphMaxTokens && nrows <= Rmax;
         if (graphable) {
-            std::vector<int> key{T, E, n_want_rows, any_fb ? 1 : 0};
+            std::vector<int> key{T, E, n_want_rows, any_fb ? 1 : 0, span};
             for (int sl : sample_slots) { key.push_back(sl); key.push_back(seqs[sl].samp_epoch); }
             StepGraph* g = nullptr;
             for (auto& e : graphs) if (e.key == key) { g = &e; break; }
@@ -405,6 +415,7 @@ struct Engine final : SeqEngine {
         for (auto& p : pieces) seqs[ents[p.ent].slot].pos += p.cnt;
     }
 
+    int cur_span = 128;
     struct StepGraph { std::vector<int> key; cudaGraphExec_t exec; uint64_t kernels; };
     std::vector<StepGraph> graphs;
     void clear_graphs() { for (auto& g : graphs) if (g.exec) cudaGraphExecDestroy(g.exec); graphs.clear(); }
@@ -419,7 +430,7 @@ struct Engine final : SeqEngine {
         if (fp32) embed_gather_any_kernel<float><<<T, 128, 0, st>>>(rb.tokens, reinterpret_cast<const float*>(embed), x, W, V);
         else embed_gather_any_kernel<__nv_bfloat16><<<T, 128, 0, st>>>(rb.tokens, reinterpret_cast<const __nv_bfloat16*>(embed), x, W, V);
         c.cnt.kernels++;
-        StepView v{this, rb, x, y};
+        StepView v{this, rb, x, y, h_meta + 4 * Tmax, h_meta + 4 * Tmax + (slots + 1), h_meta + 4 * Tmax + (slots + 1) + slots, cur_span};
         for (int l = 0; l < L; ++l) {
             LayerRec& Ly = layers[l];
             Ly.mixer->run(v);
@@ -542,7 +553,7 @@ struct Hgrn2Mixer final : Sublayer {
         state = E.c.alloc<float>(slot_stride * E.slots);
         AHA_CUDA_CHECK(cudaMemset(state, 0, slot_stride * E.slots * sizeof(float)));
         const size_t smem = hgrn2_scan_smem(D, Dv);
-        AHA_REQUIRE(smem <= 200 * 1024, "hgrn2: dim x vdim state does not fit shared memory");
+        AHA_REQUIRE((D <= 256 && E.opt.seq_impl != 1) || smem <= 200 * 1024, "hgrn2: dim x vdim state does not fit shared memory");
         AHA_CUDA_CHECK(cudaFuncSetAttribute(hgrn2_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
     }
     int proj_cols() const override { return in.N; }
@@ -554,7 +565,7 @@ struct Hgrn2Mixer final : Sublayer {
         a.qfv = E.proj; a.ld = in.N; a.lower = lower; a.norm_w = norm_w; a.eps = E.eps; a.state = state; a.slot_stride = slot_stride;
         a.out = E.inner; a.H = H; a.D = D; a.Dv = Dv; a.rb = v.rb;
         E.tic("hgrn2 recurrence", 4.0 * T * H * D * Dv, 4.0 * T * (in.N + H * Dv) + 8.0 * v.rb.E * slot_stride);
-        hgrn2_scan(E.c.stream, a); E.c.cnt.kernels++;
+        E.c.cnt.kernels += hgrn2_scan(E.c.stream, a, E.opt.seq_impl);
         E.toc();
         E.gemm(AEPI_STORE, E.inner, H * Dv, out, v.y, E.W, T);
     }
@@ -620,6 +631,7 @@ struct WindowAttentionMixer final : Sublayer {
     int proj_cols() const override { return in.N; }
     int inner_cols() const override { return H * Dv; }
     int q_cols() const override { return H * D; }
+    size_t attn_part_floats() const override { return window_attn_part_floats(H, Dv); }
     uint64_t kv_bytes_per_token() const override { return owns_kv ? 4ull * G * (D + Dv) : 0; }
     void run(const StepView& v) override {
         const int T = v.rb.T;
@@ -635,8 +647,34 @@ struct WindowAttentionMixer final : Sublayer {
         WindowAttnArgs w{};
         w.q = E.qbuf; w.kv = kv; w.slopes = slopes; w.scale = scale; w.window = window;
         w.gate = g_off >= 0 ? E.proj + g_off : nullptr; w.gate_ld = in.N; w.out = E.inner; w.H = H; w.rb = v.rb;
+        w.part = E.opt.seq_impl == 1 ? nullptr : E.attn_part;
+        // prompt portions on the tensor cores (one launch pair per entry), everything else -- decoded tokens, short portions, exact mode,
+        // other head sizes -- on the CUDA-core kernel, which skips the entries the tensor cores took
+        const bool tc = !E.fp32 && E.opt.seq_impl != 1 && D == Dv && (D == 64 || D == 128);
+        int tc_tokens = 0;
         E.tic("window attention", 2.0 * E.prof_pairs(window) * H * (D + Dv), 4.0 * (T * (double)H * (D + Dv) + E.prof_unique(window) * G * (D + Dv)));
-        window_attn(E.c.stream, w); E.c.cnt.kernels++;
+        if (tc)
+            for (int e = 0; e < v.rb.E; ++e) {
+                const int n = v.h_ent_start[e + 1] - v.h_ent_start[e], pos0 = v.h_ent_pos0[e];
+                if (n < kTcAttnMinTokens) continue;
+                FlashArgs f{};
+                f.q = E.qbuf; f.q_tok_stride = (size_t)H * D; f.q_head_stride = D;
+                f.kv.k = kv.k; f.kv.v = kv.v; f.kv.page_table = v.rb.page_tables + (size_t)v.h_ent_slot[e] * v.rb.max_pages; f.kv.page_shift = kPageShift;
+                f.kv.page_stride = (size_t)G * kPage * D; f.kv.tok_stride = D; f.kv.head_stride = (size_t)kPage * D;
+                f.out = E.inner; f.o_tok_stride = (size_t)H * Dv; f.o_head_stride = Dv;
+                f.kv0 = window > 0 ? std::max(0, pos0 - window + 1) : 0;      // keys before the first query's window are not staged
+                f.Sq = n; f.Skv = pos0 + n - f.kv0; f.q0 = v.h_ent_start[e]; f.groups = H / G; f.scaling = scale;
+                FlashWindow fw;
+                fw.window = window; fw.slopes = slopes; fw.gate = w.gate; fw.gate_tok_stride = in.N;
+                if (D == 64) flash_attn_tc<64>(E.c.stream, f, H, true, E.c.split_buf((flash_tc_ws_halfs<64>(f, H) + 1) / 2), &fw);
+                else flash_attn_tc<128>(E.c.stream, f, H, true, E.c.split_buf((flash_tc_ws_halfs<128>(f, H) + 1) / 2), &fw);
+                E.c.cnt.kernels += 2;
+                tc_tokens += n;
+            }
+        if (tc_tokens < T) {
+            w.skip_from_n = tc ? kTcAttnMinTokens : 0;
+            E.c.cnt.kernels += window_attn(E.c.stream, w, window > 0 ? std::min(window, v.span) : v.span);
+        }
         E.toc();
         E.gemm(AEPI_STORE, E.inner, H * Dv, out, v.y, E.W, T);
     }
@@ -734,7 +772,10 @@ SeqEngine* make_layered_engine(Ctx& ctx, const Json& cfg, const WeightTable& wt,
     const size_t T = e.Tmax;
     e.x = ctx.alloc<float>(T * e.W); e.y = ctx.alloc<float>(T * e.W);
     e.proj = ctx.alloc<float>(T * proj_cols); e.inner = ctx.alloc<float>(T * inner_cols); e.qbuf = ctx.alloc<float>(T * q_cols);
-    if (!e.fp32) { gemm_tc_init(); ctx.split_buf(T * (size_t)std::max({e.W, proj_cols, inner_cols})); }
+    if (!e.fp32) { gemm_tc_init(); flash_attn_tc_init(); ctx.split_buf(T * (size_t)std::max({e.W, proj_cols, inner_cols})); }
+    size_t part = 0;
+    for (auto& ly : e.layers) part = std::max(part, ly.mixer->attn_part_floats());
+    if (part) e.attn_part = ctx.alloc<float>(part);
     e.hn = ctx.alloc<float>((size_t)e.Rmax * e.W); e.logits = ctx.alloc<float>((size_t)e.Rmax * e.V);
     e.meta_ints = 4 * T + (e.slots + 1) + 2 * e.slots + (T + e.slots);
     e.d_meta = ctx.alloc<int>(e.meta_ints);

@@ -37,6 +37,7 @@ struct SeqEngineOptions {
     bool fp32 = false;            // true: weights widened to fp32 and every product in fp32; false: bf16 weights, bf16 tensor-core products where they apply
     bool use_graph = true;        // replay decode-only steps from CUDA graphs
     int gemm_impl = 0;            // 0 = auto, 1 = CUDA-core kernels only
+    int seq_impl = 0;             // sequence kernels (attention, recurrence): 0 = auto (the fast ones where the sizes allow), 1 = the plain ones only
 };
 
 class SeqEngine {

@@ -399,7 +399,7 @@ def bench_malasun(args):
                           "bound": "tensor" if v["flops"] / (tf * 1e12) > v["bytes"] / (hbm * 1e9) else "HBM"}
             rec[label] = {"tokens_per_s": round(pr["tokens_per_step"] / (pr["ms_per_step"] * 1e-3), 1), "ms_per_step": round(pr["ms_per_step"], 4),
                           "kernels_per_step": pr["kernels_per_step"], "graph_launches_per_step": pr["graph_launches_per_step"], "families": fam}
-            log(f"[malasun {name}] {label}: {rec[label]['tokens_per_s']} tok/s")
+            log(f"[malasun {name}] {label}: {rec[label]['tokens_per_s']} tok/s  " + "; ".join(f"{k}: {v['ms']} ms ({v['of_roofline']})" for k, v in sorted(fam.items())))
         m.close()
         # Qwen3 at equal size
         n_att = sum(1 for ly in cfg["layers"] if ly["type"] == "attention")
@@ -408,7 +408,7 @@ def bench_malasun(args):
                   head_dim=128, vocab_size=sz["vocab"], tie_word_embeddings=False)
         log(f"[qwen3 {name}] weights ...")
         qw = synth.make_qwen3(qc, 0, fast=True)
-        q = B200Model("qwen3", qc, qw, eos_ids=[qc.get("eos_token_id", 0)], max_ctx=4096, max_prefill=2048)
+        q = B200Model("qwen3", qc, qw, eos_ids=[qc.get("eos_token_id", 0)], max_ctx=8 * 2048 + 512, max_prefill=2048)
         del qw
         ids = synth.synth_text_ids(2048, sz["vocab"], 1)
         import torch

@@ -32,7 +32,7 @@ def R(heads=2, dim=8, vdim=8, ff=None):
 class Pair:
     """The library's handle and the oracle on the same random checkpoint."""
 
-    def __init__(self, cfg, seed=0, exact=True, max_ctx=1024, max_seqs=4, step_tokens=512, boost=None):
+    def __init__(self, cfg, seed=0, exact=True, max_ctx=1024, max_seqs=4, step_tokens=512, boost=None, plain=False):
         self.cfg = cfg
         w = synth.make_malasun(cfg, seed)
         f = {k: synth.bf16_to_f32(v) for k, v in w.items()}
@@ -40,7 +40,7 @@ class Pair:
             f["embed"] = f["embed"].copy()
             f["embed"][boost] *= 8.0
             w["embed"] = synth._bf16_round(f["embed"])
-        self.m = B200Model("malasun", cfg, w, max_ctx=max_ctx, max_prefill=step_tokens, max_seqs=max_seqs, exact_fp32=exact)
+        self.m = B200Model("malasun", cfg, w, max_ctx=max_ctx, max_prefill=step_tokens, max_seqs=max_seqs, exact_fp32=exact, attn_impl=1 if plain else 0)
         self.o = Malasun(cfg, f)
         self.tol = TOL32 if exact else TOL16
         self.V = cfg["vocab"]
@@ -130,6 +130,52 @@ def test_tensor_core_linears_in_serving_mode():
     st = p.m.stats()
     assert st["kernel_launches"] > 0
     p.close()
+
+
+def test_tensor_core_attention_in_serving_mode():
+    # head sizes 64 and 128 with dim == vdim: prompt portions of 32 tokens and more run their attention on the tcgen05 flash kernel (window,
+    # distance penalty and gate inside it), shorter portions and decoded tokens on the CUDA-core kernel; the marked token's key and value
+    # stand out, so a window that is one key off, or a tile that is skipped wrongly, moves the rows around the edges far beyond the budget
+    mark = 3
+    cfg = synth.malasun_config([A(heads=4, kv_heads=2, dim=64, vdim=64, window=100, conv=4, ff=128), R(heads=2, dim=32, vdim=16),
+                                A(heads=4, kv_heads=2, dim=64, vdim=64, window=37, conv=2, kv_from=0), A(heads=2, kv_heads=1, dim=128, vdim=128, window=None, conv=None, ff=64),
+                                A(heads=2, kv_heads=2, dim=128, vdim=128, window=130, conv=3)], width=64, vocab=90)
+    p = Pair(cfg, seed=31, exact=False, max_ctx=2048, step_tokens=1024, boost=mark)
+    ids = p.ids(700, 6, avoid=mark)
+    ids[[5, 200, 263, 455]] = mark
+    want = p.o.forward(ids)
+    for cuts in ([], [40, 45, 300, 333, 429, 461, 600], [130, 131, 194, 195, 259] + list(range(640, 700))):
+        got = p.run_cuts(ids, cuts)
+        err = np.abs(got - want).max() / want.std()
+        assert err < 3e-3, (cuts[:4], err, int(np.abs(got - want).max(axis=1).argmax()))
+    # the rows just past every window edge of a marked key depend on the edge being exact
+    other = Malasun(synth.malasun_config([A(heads=4, kv_heads=2, dim=64, vdim=64, window=101, conv=4, ff=128), R(heads=2, dim=32, vdim=16),
+                                          A(heads=4, kv_heads=2, dim=64, vdim=64, window=38, conv=2, kv_from=0), A(heads=2, kv_heads=1, dim=128, vdim=128, window=None, conv=None, ff=64),
+                                          A(heads=2, kv_heads=2, dim=128, vdim=128, window=131, conv=3)], width=64, vocab=90), p.o.w).forward(ids)
+    assert np.abs(other[300] - want[300]).max() / want.std() > 0.03        # ten times the budget above
+    p.close()
+
+
+def test_plain_kernels_agree_with_the_fast_ones():
+    cfg = synth.get_config("malasun", "tiny")
+    ids = np.random.default_rng(3).integers(0, cfg["vocab"], 300).astype(np.uint32)
+    out = []
+    for plain in (False, True):
+        p = Pair(cfg, seed=17, plain=plain)
+        out.append(p.run_cuts(ids, [70, 71, 200] + list(range(250, 300))))
+        p.check(out[-1], p.o.forward(ids), "plain kernels" if plain else "fast kernels")
+        p.close()
+    assert np.abs(out[0] - out[1]).max() <= 2 * TOL32 * max(1.0, np.abs(out[1]).std())
+
+
+def test_recurrence_sizes_beyond_one_column_slice():
+    # vdim that is no multiple of the 16-column slice, dim that is no multiple of 4 (unaligned rows), dim above 128 (several state rows per thread)
+    for layers in ([R(heads=2, dim=6, vdim=21)], [R(heads=1, dim=136, vdim=40, ff=24)], [R(heads=3, dim=20, vdim=16), R(heads=1, dim=260, vdim=8)]):
+        p = Pair(synth.malasun_config(layers, width=36, vocab=50), seed=19)
+        ids = p.ids(75, 2)
+        want = p.o.forward(ids)
+        p.check(p.run_cuts(ids, [33, 34, 66] + list(range(67, 75))), want, "recurrence sizes")
+        p.close()
 
 
 def test_launches_shorter_than_a_step_are_cut_by_the_scheduler():
