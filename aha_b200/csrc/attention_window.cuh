@@ -54,10 +54,18 @@ static __global__ void __launch_bounds__(256) qkv_conv_norm_kernel(QkvPrepArgs a
     const int ctot = a.Cq + a.Ck + a.Cv;
     const float* tail = a.tails ? a.tails + (size_t)slot * a.tail_slot_stride : nullptr;
     const bool conv = a.taps > 1;
+    // an entry of ONE token (a decoded token) moves its slot's tail along right here: the thread that convolves a channel is the only
+    // reader and writer of that channel's tail, so no second launch is needed for it
+    const bool single = conv && a.rb.ent_start[e + 1] - a.rb.ent_start[e] == 1;
     auto value = [&](const float* w, int coff, int off, int c) {
         if (!conv) return a.proj[(size_t)t * a.ld + off + c];
         float y = 0.f;
         for (int j = 0; j < a.taps; ++j) y = fmaf(w[(size_t)c * a.taps + j], conv_input(a, t, local, pos, tail, ctot, coff, off, c, a.taps - 1 - j), y);
+        if (single) {
+            float* tl = a.tails + (size_t)slot * a.tail_slot_stride + coff + c;
+            for (int r = 0; r + 2 < a.taps; ++r) tl[(size_t)r * ctot] = tl[(size_t)(r + 1) * ctot];
+            tl[(size_t)(a.taps - 2) * ctot] = a.proj[(size_t)t * a.ld + off + c];
+        }
         return y;
     };
     // q
@@ -94,6 +102,7 @@ static __global__ void __launch_bounds__(256) qkv_conv_norm_kernel(QkvPrepArgs a
 static __global__ void __launch_bounds__(256) conv_tail_update_kernel(QkvPrepArgs a) {
     const int e = blockIdx.x;
     const int t0 = a.rb.ent_start[e], n = a.rb.ent_start[e + 1] - t0, pos0 = a.rb.ent_pos0[e], slot = a.rb.ent_slot[e];
+    if (n == 1) return;      // done by the convolution kernel
     const int ctot = a.Cq + a.Ck + a.Cv, nt = a.taps - 1;
     float* tail = a.tails + (size_t)slot * a.tail_slot_stride;
     for (int c = threadIdx.x; c < ctot; c += blockDim.x) {
@@ -247,12 +256,15 @@ static __global__ void __launch_bounds__(kWinAttnThreads) window_attn_merge_kern
     }
 }
 
-inline void qkv_prepare(cudaStream_t st, const QkvPrepArgs& a) {
-    if (a.rb.T == 0) return;
+// only_single: every entry of the step brings one token (the tails are moved along by the convolution kernel).  Returns the launches.
+inline int qkv_prepare(cudaStream_t st, const QkvPrepArgs& a, bool only_single) {
+    if (a.rb.T == 0) return 0;
     AHA_REQUIRE(a.taps <= kConvMaxTaps, "short convolution: more than 16 taps");
     qkv_conv_norm_kernel<<<a.rb.T, 256, 0, st>>>(a);
-    if (a.taps > 1) conv_tail_update_kernel<<<a.rb.E, 256, 0, st>>>(a);
+    const bool tail_launch = a.taps > 1 && !only_single;
+    if (tail_launch) conv_tail_update_kernel<<<a.rb.E, 256, 0, st>>>(a);
     AHA_CUDA_CHECK(cudaGetLastError());
+    return tail_launch ? 2 : 1;
 }
 
 inline size_t window_attn_part_floats(int H, int Dv) { return (size_t)kWinSplitMaxTokens * H * kWinMaxSplits * (2 + Dv); }

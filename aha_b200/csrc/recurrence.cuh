@@ -80,8 +80,9 @@ inline size_t hgrn2_scan_smem(int D, int Dv) { return ((size_t)D * Dv + 2 * D + 
 // The serving kernels.  The columns of a head's state are independent of one another (column j sees only v[j]), so the grid is
 // (entry, head, 16-column slice) and the whole slice of the state lives in REGISTERS: thread (ig, jj) of 256 holds rows ig, ig + 16, ...
 // of column jj.  Tokens are walked in order; a chunk of 32 tokens' gates, queries and values is staged into shared memory with
-// cp.async while the previous chunk is computed (two buffers), so that the serial loop has no global load and no block barrier in
-// it: per token a thread does R fused multiply-adds on its state, R on its partial output and a 16-lane shuffle sum.
+// cp.async while the previous chunk is computed (two buffers), so that the serial loop has no global load, no shuffle and no barrier
+// in it: per token a thread does R fused multiply-adds on its state and R on its partial output; the partial outputs of a chunk are
+// summed over the 16 row groups after its last token.
 //   hgrn2_gates_kernel      q <- silu(q_raw), f <- lower + (1 - lower) sigmoid(f_raw), in place, once for all column slices
 //   hgrn2_scan_reg_kernel   the recurrence; leaves o un-normalised in `out`
 //   hgrn2_out_norm_kernel   per (token, head): o / sqrt(mean o^2 + eps) * norm_w
@@ -105,13 +106,13 @@ __device__ __forceinline__ void cp_async_f32x4(float* dst, const float* src) {
 }
 
 template <int R>   // state rows per thread: D <= 16 R
-static __global__ void __launch_bounds__(kScanThreads) hgrn2_scan_reg_kernel(Hgrn2Args a, int vec) {
+static __global__ void __launch_bounds__(kScanThreads) hgrn2_scan_reg_kernel(Hgrn2Args a, int vec, int raw) {
     extern __shared__ __align__(16) float sm[];
     const int e = blockIdx.x, h = blockIdx.y, j0 = blockIdx.z * kScanCols;
     const int D = a.D, Dv = a.Dv, HD = a.H * a.D;
     const int tid = threadIdx.x, ig = tid & 15, jj = tid >> 4, j = j0 + jj;
     const int stage_floats = kScanChunk * (2 * D + kScanCols);
-    float* oS = sm + 2 * stage_floats;               // [chunk][16]
+    float* pS = sm + 2 * stage_floats;               // [chunk][256]: every thread's partial output of a token (summed over its state rows)
     const int t0 = a.rb.ent_start[e], t1 = a.rb.ent_start[e + 1];
     const bool fresh = a.rb.ent_pos0[e] == 0;
     float* st = a.state + (size_t)a.rb.ent_slot[e] * a.slot_stride + (size_t)h * D * Dv;
@@ -127,7 +128,15 @@ static __global__ void __launch_bounds__(kScanThreads) hgrn2_scan_reg_kernel(Hgr
         float* fS = qS + kScanChunk * D;
         float* vS = fS + kScanChunk * D;
         const int tt0 = t0 + c * kScanChunk, cnt = min(kScanChunk, t1 - tt0);
-        if (vec) {
+        if (raw) {      // decode-sized steps: the gates are formed here instead of by a launch of their own
+            for (int idx = tid; idx < cnt * D; idx += kScanThreads) {
+                const int tl = idx / D, i = idx % D;
+                const float* row = a.qfv + (size_t)(tt0 + tl) * a.ld + h * D + i;
+                const float lo = a.lower[h * D + i];
+                qS[tl * D + i] = silu_f(row[0]);
+                fS[tl * D + i] = lo + (1.f - lo) * sigmoid_f(row[HD]);
+            }
+        } else if (vec) {
             const int D4 = D >> 2;
             for (int idx = tid; idx < cnt * D4; idx += kScanThreads) {
                 const int tl = idx / D4, i = (idx % D4) * 4;
@@ -159,6 +168,8 @@ static __global__ void __launch_bounds__(kScanThreads) hgrn2_scan_reg_kernel(Hgr
         const float* fS = qS + kScanChunk * D;
         const float* vS = fS + kScanChunk * D;
         const int tt0 = t0 + c * kScanChunk, cnt = min(kScanChunk, t1 - tt0);
+        // the serial part: nothing but shared-memory reads and fused multiply-adds; the sum over the 16 row groups waits for the chunk's end
+#pragma unroll 4
         for (int tl = 0; tl < cnt; ++tl) {
             const float vj = vS[tl * kScanCols + jj];
             float o = 0.f;
@@ -171,18 +182,17 @@ static __global__ void __launch_bounds__(kScanThreads) hgrn2_scan_reg_kernel(Hgr
                     o = fmaf(s[r], qS[tl * D + i], o);
                 }
             }
-            o += __shfl_xor_sync(0xffffffffu, o, 8);
-            o += __shfl_xor_sync(0xffffffffu, o, 4);
-            o += __shfl_xor_sync(0xffffffffu, o, 2);
-            o += __shfl_xor_sync(0xffffffffu, o, 1);
-            if (ig == 0) oS[tl * kScanCols + jj] = o;
+            pS[tl * kScanThreads + tid] = o;
         }
         __syncthreads();
-        for (int idx = tid; idx < cnt * kScanCols; idx += kScanThreads) {
+        for (int idx = tid; idx < cnt * kScanCols; idx += kScanThreads) {      // idx = token * 16 + column: its 16 partial sums are consecutive
+            const float4* pp = reinterpret_cast<const float4*>(pS + (size_t)idx * 16);
+            const float4 p0 = pp[0], p1 = pp[1], p2 = pp[2], p3 = pp[3];
+            const float o = ((p0.x + p0.y) + (p0.z + p0.w)) + ((p1.x + p1.y) + (p1.z + p1.w)) + ((p2.x + p2.y) + (p2.z + p2.w)) + ((p3.x + p3.y) + (p3.z + p3.w));
             const int tl = idx / kScanCols, c2 = idx % kScanCols;
-            if (j0 + c2 < Dv) a.out[(size_t)(tt0 + tl) * a.H * Dv + h * Dv + j0 + c2] = oS[idx];
+            if (j0 + c2 < Dv) a.out[(size_t)(tt0 + tl) * a.H * Dv + h * Dv + j0 + c2] = o;
         }
-        __syncthreads();       // oS and the buffer of chunk c are free again
+        __syncthreads();       // pS and the buffer of chunk c are free again
     }
 #pragma unroll
     for (int r = 0; r < R; ++r) {
@@ -203,14 +213,14 @@ static __global__ void __launch_bounds__(256) hgrn2_out_norm_kernel(float* __res
     for (int j = lane; j < Dv; j += 32) o[j] = o[j] * inv * norm_w[j];
 }
 
-inline size_t hgrn2_scan_reg_smem(int D) { return ((size_t)2 * kScanChunk * (2 * D + kScanCols) + kScanChunk * kScanCols) * sizeof(float); }
+inline size_t hgrn2_scan_reg_smem(int D) { return ((size_t)2 * kScanChunk * (2 * D + kScanCols) + kScanChunk * kScanThreads) * sizeof(float); }
 
 template <int R>
-inline void hgrn2_scan_reg_launch(cudaStream_t st, const Hgrn2Args& a, int vec) {
+inline void hgrn2_scan_reg_launch(cudaStream_t st, const Hgrn2Args& a, int vec, int raw) {
     static bool attr = false;
     const size_t smem = hgrn2_scan_reg_smem(a.D);
     if (!attr) { AHA_CUDA_CHECK(cudaFuncSetAttribute(hgrn2_scan_reg_kernel<R>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)hgrn2_scan_reg_smem(16 * R))); attr = true; }
-    hgrn2_scan_reg_kernel<R><<<dim3(a.rb.E, a.H, (a.Dv + kScanCols - 1) / kScanCols), kScanThreads, smem, st>>>(a, vec);
+    hgrn2_scan_reg_kernel<R><<<dim3(a.rb.E, a.H, (a.Dv + kScanCols - 1) / kScanCols), kScanThreads, smem, st>>>(a, vec, raw);
 }
 
 // impl 0: the register kernels (dim <= 256); 1: the plain shared-memory kernel above.  `qfv` is overwritten by the gates (impl 0).  Returns launches.
@@ -223,17 +233,18 @@ inline int hgrn2_scan(cudaStream_t st, const Hgrn2Args& a, int impl = 0) {
         return 1;
     }
     const int HD = a.H * a.D, T = a.rb.T;
-    hgrn2_gates_kernel<<<(unsigned)(((size_t)T * HD + 255) / 256), 256, 0, st>>>(const_cast<float*>(a.qfv), a.ld, a.lower, HD, T);
+    const int raw = T <= 32 ? 1 : 0;     // few tokens: every column slice forms the gates itself (one launch less); else once, in place
+    if (!raw) hgrn2_gates_kernel<<<(unsigned)(((size_t)T * HD + 255) / 256), 256, 0, st>>>(const_cast<float*>(a.qfv), a.ld, a.lower, HD, T);
     const int vec = (a.D % 4 == 0 && a.ld % 4 == 0 && (reinterpret_cast<uintptr_t>(a.qfv) & 15) == 0) ? 1 : 0;
     const int R = (a.D + 15) / 16;
-    if (R <= 1) hgrn2_scan_reg_launch<1>(st, a, vec);
-    else if (R <= 2) hgrn2_scan_reg_launch<2>(st, a, vec);
-    else if (R <= 4) hgrn2_scan_reg_launch<4>(st, a, vec);
-    else if (R <= 8) hgrn2_scan_reg_launch<8>(st, a, vec);
-    else hgrn2_scan_reg_launch<16>(st, a, vec);
+    if (R <= 1) hgrn2_scan_reg_launch<1>(st, a, vec, raw);
+    else if (R <= 2) hgrn2_scan_reg_launch<2>(st, a, vec, raw);
+    else if (R <= 4) hgrn2_scan_reg_launch<4>(st, a, vec, raw);
+    else if (R <= 8) hgrn2_scan_reg_launch<8>(st, a, vec, raw);
+    else hgrn2_scan_reg_launch<16>(st, a, vec, raw);
     hgrn2_out_norm_kernel<<<(unsigned)(((size_t)T * a.H * 32 + 255) / 256), 256, 0, st>>>(a.out, a.norm_w, a.eps, T * a.H, a.Dv);
     AHA_CUDA_CHECK(cudaGetLastError());
-    return 3;
+    return raw ? 2 : 3;
 }
 
 }  // namespace aha

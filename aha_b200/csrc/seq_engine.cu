@@ -642,7 +642,7 @@ struct WindowAttentionMixer final : Sublayer {
         a.taps = taps; a.wq = wq; a.wk = wk; a.wv = wv; a.tails = tails; a.tail_slot_stride = tail_stride;
         a.q_norm = q_norm; a.k_norm = k_norm; a.eps = E.eps; a.q_out = E.qbuf; a.kv = kv; a.rb = v.rb;
         E.tic("conv + q/k norm + cache write", 2.0 * T * (a.Cq + a.Ck + a.Cv) * std::max(1, taps), 4.0 * T * (2.0 * a.Cq + 2.0 * a.Ck + 2.0 * a.Cv));
-        qkv_prepare(E.c.stream, a); E.c.cnt.kernels += taps > 1 ? 2 : 1;
+        E.c.cnt.kernels += qkv_prepare(E.c.stream, a, v.rb.E == T);
         E.toc();
         WindowAttnArgs w{};
         w.q = E.qbuf; w.kv = kv; w.slopes = slopes; w.scale = scale; w.window = window;
