@@ -26,7 +26,20 @@ struct Hgrn2Args {
     float* out;            // [T, H*Dv]
     int H, D, Dv;
     RaggedBatch rb;
+    // long prompt portions cut into segments that are scanned side by side (see hgrn2_scan); all unset: every entry is walked whole
+    float* seg_state = nullptr;   // [segments of the step][H][D][Dv]
+    float* seg_decay = nullptr;   // [segments of the step][H*D]
+    int seg_len = 0;              // tokens per segment
+    int seg_max = 0;              // segments of the step's longest entry
 };
+
+// Segments of a step are numbered entry by entry; an entry has at least one.
+__device__ __forceinline__ int hgrn2_seg_count(const RaggedBatch& rb, int e, int L) { return max(1, (rb.ent_start[e + 1] - rb.ent_start[e] + L - 1) / L); }
+__device__ __forceinline__ int hgrn2_seg_base(const RaggedBatch& rb, int e, int L) {
+    int b = 0;
+    for (int i = 0; i < e; ++i) b += hgrn2_seg_count(rb, i, L);
+    return b;
+}
 
 // Generic version: the head's state lives in shared memory ([D][Dv] floats), thread j owns column j (and j + blockDim, ...).
 static __global__ void hgrn2_scan_kernel(Hgrn2Args a) {
@@ -78,15 +91,18 @@ inline size_t hgrn2_scan_smem(int D, int Dv) { return ((size_t)D * Dv + 2 * D + 
 
 // ---------------------------------------------------------------------------------------------------------------------------------
 // The serving kernels.  The columns of a head's state are independent of one another (column j sees only v[j]), so the grid is
-// (entry, head, 16-column slice) and the whole slice of the state lives in REGISTERS: thread (ig, jj) of 256 holds rows ig, ig + 16, ...
-// of column jj.  Tokens are walked in order; a chunk of 32 tokens' gates, queries and values is staged into shared memory with
-// cp.async while the previous chunk is computed (two buffers), so that the serial loop has no global load, no shuffle and no barrier
-// in it: per token a thread does R fused multiply-adds on its state and R on its partial output; the partial outputs of a chunk are
+// (entry, head, 32-column slice) and the whole slice of the state lives in REGISTERS: thread (ig, jj) of 256 holds, of the columns jj and
+// jj + 16, the rows 4 ig .. 4 ig + 3 of every block of 64 rows.  A gate or query value read from shared memory (16 bytes = four rows a
+// load) thus serves two columns, and the 16 threads of one column read 256 consecutive bytes.  Tokens are walked in order; a chunk of
+// 16 tokens' gates, queries and values is staged into shared memory with cp.async while the previous chunk is computed (two buffers;
+// rows are padded to 16 R with f = 1, q = 0), so that the serial loop has no global load, no shuffle, no barrier and no predicate in
+// it: per token a thread does 2 R fused multiply-adds on its state and 2 R on its partial outputs; the partial outputs of a chunk are
 // summed over the 16 row groups after its last token.
 //   hgrn2_gates_kernel      q <- silu(q_raw), f <- lower + (1 - lower) sigmoid(f_raw), in place, once for all column slices
 //   hgrn2_scan_reg_kernel   the recurrence; leaves o un-normalised in `out`
 //   hgrn2_out_norm_kernel   per (token, head): o / sqrt(mean o^2 + eps) * norm_w
-constexpr int kScanCols = 16, kScanChunk = 32, kScanThreads = 256;
+constexpr int kScanCols = 32, kScanChunk = 16, kScanThreads = 256;
+constexpr int kScanPad = 20;     // floats between the partial-output groups of two columns: 16 + 4, so that the 16-byte reads of the sum spread over the banks
 
 static __global__ void hgrn2_gates_kernel(float* __restrict__ qfv, int ld, const float* __restrict__ lower, int HD, int T) {
     const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -105,51 +121,78 @@ __device__ __forceinline__ void cp_async_f32x4(float* dst, const float* src) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
 }
 
-template <int R>   // state rows per thread: D <= 16 R
+template <int R>   // state rows per thread and column, a multiple of 4: D <= 16 R
 static __global__ void __launch_bounds__(kScanThreads) hgrn2_scan_reg_kernel(Hgrn2Args a, int vec, int raw) {
     extern __shared__ __align__(16) float sm[];
-    const int e = blockIdx.x, h = blockIdx.y, j0 = blockIdx.z * kScanCols;
+    constexpr int Dp = 16 * R, R4 = R / 4;
+    const int h = blockIdx.y, j0 = blockIdx.z * kScanCols;
     const int D = a.D, Dv = a.Dv, HD = a.H * a.D;
-    const int tid = threadIdx.x, ig = tid & 15, jj = tid >> 4, j = j0 + jj;
-    const int stage_floats = kScanChunk * (2 * D + kScanCols);
-    float* pS = sm + 2 * stage_floats;               // [chunk][256]: every thread's partial output of a token (summed over its state rows)
-    const int t0 = a.rb.ent_start[e], t1 = a.rb.ent_start[e + 1];
-    const bool fresh = a.rb.ent_pos0[e] == 0;
-    float* st = a.state + (size_t)a.rb.ent_slot[e] * a.slot_stride + (size_t)h * D * Dv;
-    float s[R];
+    const int tid = threadIdx.x, ig = tid & 15, jj = tid >> 4;
+    constexpr int stage_floats = kScanChunk * (2 * Dp + kScanCols);
+    float* pS = sm + 2 * stage_floats;               // [chunk][32 columns][kScanPad]: every thread's partial outputs of a token (summed over its state rows)
+    int e = blockIdx.x, t0, t1;
+    bool fresh;
+    const float* st_in;
+    float* st;
+    if (a.seg_len > 0) {      // segment k of entry e: from the slot's state (k == 0) or from zero, to the segment's scratch
+        e = blockIdx.x / a.seg_max;
+        const int k = blockIdx.x % a.seg_max;
+        if (k >= hgrn2_seg_count(a.rb, e, a.seg_len)) return;
+        t0 = a.rb.ent_start[e] + k * a.seg_len;
+        t1 = min(a.rb.ent_start[e + 1], t0 + a.seg_len);
+        fresh = k > 0 || a.rb.ent_pos0[e] == 0;
+        st_in = a.state + (size_t)a.rb.ent_slot[e] * a.slot_stride + (size_t)h * D * Dv;
+        st = a.seg_state + ((size_t)(hgrn2_seg_base(a.rb, e, a.seg_len) + k) * a.H + h) * D * Dv;
+    } else {
+        t0 = a.rb.ent_start[e]; t1 = a.rb.ent_start[e + 1];
+        fresh = a.rb.ent_pos0[e] == 0;
+        st = a.state + (size_t)a.rb.ent_slot[e] * a.slot_stride + (size_t)h * D * Dv;
+        st_in = st;
+    }
+    auto row_of = [&](int r) { return (r >> 2) * 64 + 4 * ig + (r & 3); };
+    float s[R][2];
 #pragma unroll
-    for (int r = 0; r < R; ++r) {
-        const int i = ig + 16 * r;
-        s[r] = (!fresh && i < D && j < Dv) ? st[(size_t)i * Dv + j] : 0.f;
+    for (int r = 0; r < R; ++r)
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+            const int i = row_of(r), j = j0 + 16 * c + jj;
+            s[r][c] = (!fresh && i < D && j < Dv) ? st_in[(size_t)i * Dv + j] : 0.f;
+        }
+    // rows beyond `dim` of both buffers: f = 1, q = 0 (their state stays zero); no copy below touches them
+    for (int idx = tid; idx < 2 * kScanChunk * (Dp - D); idx += kScanThreads) {
+        const int b = idx / (kScanChunk * (Dp - D)), rem = idx % (kScanChunk * (Dp - D)), tl = rem / (Dp - D), i = D + rem % (Dp - D);
+        float* qS = sm + b * stage_floats;
+        qS[tl * Dp + i] = 0.f;
+        qS[kScanChunk * Dp + tl * Dp + i] = 1.f;
     }
     const int nch = (t1 - t0 + kScanChunk - 1) / kScanChunk;
     auto stage = [&](int c) {
         float* qS = sm + (c & 1) * stage_floats;
-        float* fS = qS + kScanChunk * D;
-        float* vS = fS + kScanChunk * D;
+        float* fS = qS + kScanChunk * Dp;
+        float* vS = fS + kScanChunk * Dp;
         const int tt0 = t0 + c * kScanChunk, cnt = min(kScanChunk, t1 - tt0);
         if (raw) {      // decode-sized steps: the gates are formed here instead of by a launch of their own
             for (int idx = tid; idx < cnt * D; idx += kScanThreads) {
                 const int tl = idx / D, i = idx % D;
                 const float* row = a.qfv + (size_t)(tt0 + tl) * a.ld + h * D + i;
                 const float lo = a.lower[h * D + i];
-                qS[tl * D + i] = silu_f(row[0]);
-                fS[tl * D + i] = lo + (1.f - lo) * sigmoid_f(row[HD]);
+                qS[tl * Dp + i] = silu_f(row[0]);
+                fS[tl * Dp + i] = lo + (1.f - lo) * sigmoid_f(row[HD]);
             }
         } else if (vec) {
             const int D4 = D >> 2;
             for (int idx = tid; idx < cnt * D4; idx += kScanThreads) {
                 const int tl = idx / D4, i = (idx % D4) * 4;
                 const float* row = a.qfv + (size_t)(tt0 + tl) * a.ld + h * D + i;
-                cp_async_f32x4(qS + tl * D + i, row);
-                cp_async_f32x4(fS + tl * D + i, row + HD);
+                cp_async_f32x4(qS + tl * Dp + i, row);
+                cp_async_f32x4(fS + tl * Dp + i, row + HD);
             }
         } else {
             for (int idx = tid; idx < cnt * D; idx += kScanThreads) {
                 const int tl = idx / D, i = idx % D;
                 const float* row = a.qfv + (size_t)(tt0 + tl) * a.ld + h * D + i;
-                cp_async_f32(qS + tl * D + i, row);
-                cp_async_f32(fS + tl * D + i, row + HD);
+                cp_async_f32(qS + tl * Dp + i, row);
+                cp_async_f32(fS + tl * Dp + i, row + HD);
             }
         }
         for (int idx = tid; idx < cnt * kScanCols; idx += kScanThreads) {
@@ -165,29 +208,67 @@ static __global__ void __launch_bounds__(kScanThreads) hgrn2_scan_reg_kernel(Hgr
         else asm volatile("cp.async.wait_group 0;" ::: "memory");
         __syncthreads();
         const float* qS = sm + (c & 1) * stage_floats;
-        const float* fS = qS + kScanChunk * D;
-        const float* vS = fS + kScanChunk * D;
+        const float* fS = qS + kScanChunk * Dp;
+        const float* vS = fS + kScanChunk * Dp;
         const int tt0 = t0 + c * kScanChunk, cnt = min(kScanChunk, t1 - tt0);
-        // the serial part: nothing but shared-memory reads and fused multiply-adds; the sum over the 16 row groups waits for the chunk's end
-#pragma unroll 4
-        for (int tl = 0; tl < cnt; ++tl) {
-            const float vj = vS[tl * kScanCols + jj];
-            float o = 0.f;
+        // the serial part: nothing but shared-memory reads and fused multiply-adds.  Tokens are taken G at a time with all loads of the
+        // group ahead of its arithmetic (the stores of partial outputs would otherwise fence the next token's loads).  The sum over the
+        // 16 row groups waits for the chunk's end.
+        {
+            constexpr int G = R >= 16 ? 1 : 2;
+            const float4* fp = reinterpret_cast<const float4*>(fS) + ig;
+            const float4* qp = reinterpret_cast<const float4*>(qS) + ig;
+            const float* vp = vS + jj;
+            float* pp = pS + jj * kScanPad + ig;
+            auto token = [&](const float4* fv, const float4* qv, float v0, float v1, int tl) {
+                float o0 = 0.f, o1 = 0.f;
 #pragma unroll
-            for (int r = 0; r < R; ++r) {
-                const int i = ig + 16 * r;
-                if (i < D) {
-                    const float f = fS[tl * D + i];
-                    s[r] = fmaf(f, s[r], (1.f - f) * vj);
-                    o = fmaf(s[r], qS[tl * D + i], o);
+                for (int r4 = 0; r4 < R4; ++r4) {
+                    const float f[4] = {fv[r4].x, fv[r4].y, fv[r4].z, fv[r4].w}, q[4] = {qv[r4].x, qv[r4].y, qv[r4].z, qv[r4].w};
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        const float g = 1.f - f[u];
+                        float* sr = s[4 * r4 + u];
+                        sr[0] = fmaf(f[u], sr[0], g * v0);
+                        sr[1] = fmaf(f[u], sr[1], g * v1);
+                        o0 = fmaf(sr[0], q[u], o0);
+                        o1 = fmaf(sr[1], q[u], o1);
+                    }
                 }
+                pp[tl * (kScanCols * kScanPad)] = o0;
+                pp[tl * (kScanCols * kScanPad) + 16 * kScanPad] = o1;
+            };
+            int tl = 0;
+            for (; tl + G <= cnt; tl += G) {
+                float4 fv[G][R4], qv[G][R4];
+                float v0[G], v1[G];
+#pragma unroll
+                for (int u = 0; u < G; ++u) {
+                    v0[u] = vp[(tl + u) * kScanCols];
+                    v1[u] = vp[(tl + u) * kScanCols + 16];
+#pragma unroll
+                    for (int r4 = 0; r4 < R4; ++r4) {
+                        fv[u][r4] = fp[(tl + u) * (Dp / 4) + 16 * r4];
+                        qv[u][r4] = qp[(tl + u) * (Dp / 4) + 16 * r4];
+                    }
+                }
+#pragma unroll
+                for (int u = 0; u < G; ++u) token(fv[u], qv[u], v0[u], v1[u], tl + u);
             }
-            pS[tl * kScanThreads + tid] = o;
+            for (; tl < cnt; ++tl) {
+                float4 fv[R4], qv[R4];
+#pragma unroll
+                for (int r4 = 0; r4 < R4; ++r4) {
+                    fv[r4] = fp[tl * (Dp / 4) + 16 * r4];
+                    qv[r4] = qp[tl * (Dp / 4) + 16 * r4];
+                }
+                token(fv, qv, vp[tl * kScanCols], vp[tl * kScanCols + 16], tl);
+            }
         }
         __syncthreads();
-        for (int idx = tid; idx < cnt * kScanCols; idx += kScanThreads) {      // idx = token * 16 + column: its 16 partial sums are consecutive
-            const float4* pp = reinterpret_cast<const float4*>(pS + (size_t)idx * 16);
-            const float4 p0 = pp[0], p1 = pp[1], p2 = pp[2], p3 = pp[3];
+        for (int idx = tid; idx < cnt * kScanCols; idx += kScanThreads) {      // idx = token * 32 + column: its 16 partial sums are consecutive
+            const float4* pq = reinterpret_cast<const float4*>(pS + (size_t)idx * kScanPad);
+            const float4 p0 = pq[0], p1 = pq[1], p2 = pq[2], p3 = pq[3];
             const float o = ((p0.x + p0.y) + (p0.z + p0.w)) + ((p1.x + p1.y) + (p1.z + p1.w)) + ((p2.x + p2.y) + (p2.z + p2.w)) + ((p3.x + p3.y) + (p3.z + p3.w));
             const int tl = idx / kScanCols, c2 = idx % kScanCols;
             if (j0 + c2 < Dv) a.out[(size_t)(tt0 + tl) * a.H * Dv + h * Dv + j0 + c2] = o;
@@ -195,10 +276,12 @@ static __global__ void __launch_bounds__(kScanThreads) hgrn2_scan_reg_kernel(Hgr
         __syncthreads();       // pS and the buffer of chunk c are free again
     }
 #pragma unroll
-    for (int r = 0; r < R; ++r) {
-        const int i = ig + 16 * r;
-        if (i < D && j < Dv) st[(size_t)i * Dv + j] = s[r];
-    }
+    for (int r = 0; r < R; ++r)
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+            const int i = row_of(r), j = j0 + 16 * c + jj;
+            if (i < D && j < Dv) st[(size_t)i * Dv + j] = s[r][c];
+        }
 }
 
 // one warp per (token, head) row of `out`
@@ -213,17 +296,109 @@ static __global__ void __launch_bounds__(256) hgrn2_out_norm_kernel(float* __res
     for (int j = lane; j < Dv; j += 32) o[j] = o[j] * inv * norm_w[j];
 }
 
-inline size_t hgrn2_scan_reg_smem(int D) { return ((size_t)2 * kScanChunk * (2 * D + kScanCols) + kScanChunk * kScanThreads) * sizeof(float); }
+// ---------------------------------------------------------------------------------------------------------------------------------
+// Long prompt portions.  The recurrence is linear in the state with a diagonal decay, so an entry can be cut into segments that are
+// scanned side by side, each from a zero state (the first from the slot's state).  With A_t[i] = f_{t0}[i] ... f_t[i], the product of
+// the gates from the segment's first token t0 to t, and S0 the state before t0,
+//     S_t = diag(A_t) S0 + S_t(from zero)      and so      o_t = o_t(from zero) + S0^T (A_t * q_t).
+// Products of gates only shrink, so nothing is ever divided by a decay and nothing overflows; a product that underflows to zero is the
+// right limit.  Four launches after the gates:
+//   hgrn2_scan_reg_kernel       every segment from zero: local outputs, the segment's local end state into scratch
+//   hgrn2_seg_decay_kernel      q_t <- A_t * q_t in place (segments after an entry's first), the segment's whole product into scratch
+//   hgrn2_seg_combine_kernel    walks an entry's segments in order: scratch <- the state BEFORE the segment, slot <- the end state
+//   hgrn2_seg_apply_kernel      out_t += S0^T (A_t * q_t), fp32 on the CUDA cores, a (64 tokens x 32 columns) tile per block
+constexpr int kSegLen = 64;         // the shortest segment; segments are a power-of-two multiple of it (and so of kScanChunk)
+constexpr int kSegLenMax = 256;
+constexpr int kSegMinEntry = 256;   // a step whose longest entry has fewer tokens walks its entries whole
+
+static __global__ void hgrn2_seg_decay_kernel(Hgrn2Args a) {
+    const int e = blockIdx.x / a.seg_max, k = blockIdx.x % a.seg_max, h = blockIdx.y, i = threadIdx.x;
+    if (k == 0 || k >= hgrn2_seg_count(a.rb, e, a.seg_len) || i >= a.D) return;
+    const int HD = a.H * a.D;
+    const int t0 = a.rb.ent_start[e] + k * a.seg_len, t1 = min(a.rb.ent_start[e + 1], t0 + a.seg_len);
+    float* q = const_cast<float*>(a.qfv) + (size_t)t0 * a.ld + h * a.D + i;
+    float prod = 1.f;
+    for (int t = t0; t < t1; ++t, q += a.ld) {
+        prod *= q[HD];
+        q[0] *= prod;
+    }
+    a.seg_decay[(size_t)(hgrn2_seg_base(a.rb, e, a.seg_len) + k) * HD + h * a.D + i] = prod;
+}
+
+static __global__ void hgrn2_seg_combine_kernel(Hgrn2Args a) {
+    const int e = blockIdx.y;
+    const size_t n = (size_t)a.H * a.D * a.Dv, idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= n) return;
+    const int nseg = hgrn2_seg_count(a.rb, e, a.seg_len), base = hgrn2_seg_base(a.rb, e, a.seg_len);
+    const size_t row = idx / a.Dv;       // head * D + state row
+    float* p = a.seg_state + (size_t)base * n + idx;
+    const float* dec = a.seg_decay + (size_t)base * a.H * a.D + row;
+    float S = p[0];
+    for (int k = 1; k < nseg; k += 8) {      // eight segments' loads ahead of the chain of multiply-adds and the stores
+        float loc[8], d[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u)
+            if (k + u < nseg) { loc[u] = p[(size_t)(k + u) * n]; d[u] = dec[(size_t)(k + u) * a.H * a.D]; }
+#pragma unroll
+        for (int u = 0; u < 8; ++u)
+            if (k + u < nseg) { p[(size_t)(k + u) * n] = S; S = fmaf(d[u], S, loc[u]); }
+    }
+    a.state[(size_t)a.rb.ent_slot[e] * a.slot_stride + idx] = S;
+}
+
+static __global__ void __launch_bounds__(256) hgrn2_seg_apply_kernel(Hgrn2Args a) {
+    __shared__ float Ss[64][32];
+    __shared__ __align__(16) float Qs[64][64];
+    const int e = blockIdx.x / a.seg_max, k = blockIdx.x % a.seg_max, h = blockIdx.y;
+    if (k == 0 || k >= hgrn2_seg_count(a.rb, e, a.seg_len)) return;
+    const int D = a.D, Dv = a.Dv, tid = threadIdx.x, tg = tid >> 5, jl = tid & 31, j = blockIdx.z * 32 + jl;
+    const int t0 = a.rb.ent_start[e] + k * a.seg_len, t1 = min(a.rb.ent_start[e + 1], t0 + a.seg_len);
+    const float* S0 = a.seg_state + ((size_t)(hgrn2_seg_base(a.rb, e, a.seg_len) + k) * a.H + h) * D * Dv;
+    for (int tt = t0; tt < t1; tt += 64) {
+        float acc[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) acc[u] = 0.f;
+        for (int i0 = 0; i0 < D; i0 += 64) {
+            for (int idx = tid; idx < 64 * 32; idx += 256) {
+                const int ii = idx >> 5, jc = blockIdx.z * 32 + (idx & 31);
+                Ss[ii][idx & 31] = (i0 + ii < D && jc < Dv) ? S0[(size_t)(i0 + ii) * Dv + jc] : 0.f;
+            }
+            for (int idx = tid; idx < 64 * 64; idx += 256) {
+                const int tl = idx >> 6, ii = idx & 63;
+                Qs[tl][ii] = (tt + tl < t1 && i0 + ii < D) ? a.qfv[(size_t)(tt + tl) * a.ld + h * D + i0 + ii] : 0.f;
+            }
+            __syncthreads();
+#pragma unroll 4
+            for (int ii = 0; ii < 64; ii += 4) {
+                const float s0 = Ss[ii][jl], s1 = Ss[ii + 1][jl], s2 = Ss[ii + 2][jl], s3 = Ss[ii + 3][jl];
+#pragma unroll
+                for (int u = 0; u < 8; ++u) {
+                    const float4 q = *reinterpret_cast<const float4*>(&Qs[tg * 8 + u][ii]);
+                    acc[u] = fmaf(s3, q.w, fmaf(s2, q.z, fmaf(s1, q.y, fmaf(s0, q.x, acc[u]))));
+                }
+            }
+            __syncthreads();
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const int t = tt + tg * 8 + u;
+            if (t < t1 && j < Dv) a.out[(size_t)t * a.H * Dv + h * Dv + j] += acc[u];
+        }
+    }
+}
+
+inline size_t hgrn2_scan_reg_smem(int R) { return ((size_t)2 * kScanChunk * (2 * 16 * R + kScanCols) + kScanChunk * kScanCols * kScanPad) * sizeof(float); }
 
 template <int R>
 inline void hgrn2_scan_reg_launch(cudaStream_t st, const Hgrn2Args& a, int vec, int raw) {
     static bool attr = false;
-    const size_t smem = hgrn2_scan_reg_smem(a.D);
-    if (!attr) { AHA_CUDA_CHECK(cudaFuncSetAttribute(hgrn2_scan_reg_kernel<R>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)hgrn2_scan_reg_smem(16 * R))); attr = true; }
-    hgrn2_scan_reg_kernel<R><<<dim3(a.rb.E, a.H, (a.Dv + kScanCols - 1) / kScanCols), kScanThreads, smem, st>>>(a, vec, raw);
+    const size_t smem = hgrn2_scan_reg_smem(R);
+    if (!attr) { AHA_CUDA_CHECK(cudaFuncSetAttribute(hgrn2_scan_reg_kernel<R>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); attr = true; }
+    hgrn2_scan_reg_kernel<R><<<dim3(a.seg_len > 0 ? a.rb.E * a.seg_max : a.rb.E, a.H, (a.Dv + kScanCols - 1) / kScanCols), kScanThreads, smem, st>>>(a, vec, raw);
 }
 
 // impl 0: the register kernels (dim <= 256); 1: the plain shared-memory kernel above.  `qfv` is overwritten by the gates (impl 0).  Returns launches.
+// With seg_len > 0 (the caller found an entry of at least kSegMinEntry tokens and gives scratch for the step's segments) entries are cut into segments.
 inline int hgrn2_scan(cudaStream_t st, const Hgrn2Args& a, int impl = 0) {
     if (a.rb.E == 0) return 0;
     if (impl == 1 || a.D > 256) {
@@ -233,18 +408,24 @@ inline int hgrn2_scan(cudaStream_t st, const Hgrn2Args& a, int impl = 0) {
         return 1;
     }
     const int HD = a.H * a.D, T = a.rb.T;
-    const int raw = T <= 32 ? 1 : 0;     // few tokens: every column slice forms the gates itself (one launch less); else once, in place
+    const bool seg = a.seg_len > 0;
+    const int raw = (T <= 32 && !seg) ? 1 : 0;     // few tokens: every column slice forms the gates itself (one launch less); else once, in place
     if (!raw) hgrn2_gates_kernel<<<(unsigned)(((size_t)T * HD + 255) / 256), 256, 0, st>>>(const_cast<float*>(a.qfv), a.ld, a.lower, HD, T);
     const int vec = (a.D % 4 == 0 && a.ld % 4 == 0 && (reinterpret_cast<uintptr_t>(a.qfv) & 15) == 0) ? 1 : 0;
     const int R = (a.D + 15) / 16;
-    if (R <= 1) hgrn2_scan_reg_launch<1>(st, a, vec, raw);
-    else if (R <= 2) hgrn2_scan_reg_launch<2>(st, a, vec, raw);
-    else if (R <= 4) hgrn2_scan_reg_launch<4>(st, a, vec, raw);
+    if (R <= 4) hgrn2_scan_reg_launch<4>(st, a, vec, raw);
     else if (R <= 8) hgrn2_scan_reg_launch<8>(st, a, vec, raw);
     else hgrn2_scan_reg_launch<16>(st, a, vec, raw);
+    if (seg) {
+        const unsigned segs = (unsigned)(a.rb.E * a.seg_max);
+        hgrn2_seg_decay_kernel<<<dim3(segs, a.H), ((a.D + 31) / 32) * 32, 0, st>>>(a);
+        const size_t n = (size_t)a.H * a.D * a.Dv;
+        hgrn2_seg_combine_kernel<<<dim3((unsigned)((n + 255) / 256), a.rb.E), 256, 0, st>>>(a);
+        hgrn2_seg_apply_kernel<<<dim3(segs, a.H, (a.Dv + 31) / 32), 256, 0, st>>>(a);
+    }
     hgrn2_out_norm_kernel<<<(unsigned)(((size_t)T * a.H * 32 + 255) / 256), 256, 0, st>>>(a.out, a.norm_w, a.eps, T * a.H, a.Dv);
     AHA_CUDA_CHECK(cudaGetLastError());
-    return raw ? 2 : 3;
+    return (raw ? 2 : 3) + (seg ? 3 : 0);
 }
 
 }  // namespace aha

@@ -65,6 +65,8 @@ struct Sublayer {
     virtual int inner_cols() const = 0;    // ... in Engine::inner
     virtual int q_cols() const { return 0; }
     virtual size_t attn_part_floats() const { return 0; }     // workspace of the split attention launches
+    virtual size_t seg_state_floats() const { return 0; }     // scratch of a recurrence that cuts long prompt portions into segments: states,
+    virtual size_t seg_decay_floats() const { return 0; }     // ... and the segments' decay products
     virtual uint64_t kv_bytes_per_token() const { return 0; }
 };
 
@@ -91,7 +93,7 @@ struct Engine final : SeqEngine {
     std::vector<Seq> seqs;
     // step scratch
     int Tmax = 0, Rmax = 0;
-    float *x = nullptr, *y = nullptr, *proj = nullptr, *inner = nullptr, *qbuf = nullptr, *hn = nullptr, *logits = nullptr, *attn_part = nullptr;
+    float *x = nullptr, *y = nullptr, *proj = nullptr, *inner = nullptr, *qbuf = nullptr, *hn = nullptr, *logits = nullptr, *attn_part = nullptr, *seg_state = nullptr, *seg_decay = nullptr;
     int* d_meta = nullptr; int* h_meta = nullptr; size_t meta_ints = 0;
     cudaEvent_t ev_meta = nullptr; bool meta_pending = false;
     // sampler state per slot
@@ -558,12 +560,24 @@ struct Hgrn2Mixer final : Sublayer {
     }
     int proj_cols() const override { return in.N; }
     int inner_cols() const override { return H * Dv; }
+    int max_segments() const { return E.Tmax / kSegLen + E.slots; }      // of one step: every entry has at most one segment that is not full
+    size_t seg_state_floats() const override { return E.Tmax >= kSegMinEntry ? (size_t)max_segments() * slot_stride : 0; }
+    size_t seg_decay_floats() const override { return E.Tmax >= kSegMinEntry ? (size_t)max_segments() * H * D : 0; }
     void run(const StepView& v) override {
         const int T = v.rb.T;
         E.gemm(AEPI_STORE, v.x, E.W, in, E.proj, in.N, T);
         Hgrn2Args a{};
         a.qfv = E.proj; a.ld = in.N; a.lower = lower; a.norm_w = norm_w; a.eps = E.eps; a.state = state; a.slot_stride = slot_stride;
         a.out = E.inner; a.H = H; a.D = D; a.Dv = Dv; a.rb = v.rb;
+        int longest = 0;
+        for (int e = 0; e < v.rb.E; ++e) longest = std::max(longest, v.h_ent_start[e + 1] - v.h_ent_start[e]);
+        if (longest >= kSegMinEntry && E.seg_state && E.opt.seq_impl == 0) {      // long prompt portions: segments scanned side by side
+            // the shortest segments that still give every SM several blocks: a segment costs a pass over the head's state
+            const int per_seg = H * ((Dv + kScanCols - 1) / kScanCols);
+            int L = kSegLen;
+            while (L < kSegLenMax && (longest / (2 * L)) * per_seg >= 8 * E.c.num_sms) L *= 2;
+            if (longest > L) { a.seg_state = E.seg_state; a.seg_decay = E.seg_decay; a.seg_len = L; a.seg_max = (longest + L - 1) / L; }
+        }
         E.tic("hgrn2 recurrence", 4.0 * T * H * D * Dv, 4.0 * T * (in.N + H * Dv) + 8.0 * v.rb.E * slot_stride);
         E.c.cnt.kernels += hgrn2_scan(E.c.stream, a, E.opt.seq_impl);
         E.toc();
@@ -776,6 +790,9 @@ SeqEngine* make_layered_engine(Ctx& ctx, const Json& cfg, const WeightTable& wt,
     size_t part = 0;
     for (auto& ly : e.layers) part = std::max(part, ly.mixer->attn_part_floats());
     if (part) e.attn_part = ctx.alloc<float>(part);
+    size_t seg_s = 0, seg_d = 0;
+    for (auto& ly : e.layers) { seg_s = std::max(seg_s, ly.mixer->seg_state_floats()); seg_d = std::max(seg_d, ly.mixer->seg_decay_floats()); }
+    if (seg_s) { e.seg_state = ctx.alloc<float>(seg_s); e.seg_decay = ctx.alloc<float>(seg_d); }
     e.hn = ctx.alloc<float>((size_t)e.Rmax * e.W); e.logits = ctx.alloc<float>((size_t)e.Rmax * e.V);
     e.meta_ints = 4 * T + (e.slots + 1) + 2 * e.slots + (T + e.slots);
     e.d_meta = ctx.alloc<int>(e.meta_ints);

@@ -32,7 +32,7 @@ def R(heads=2, dim=8, vdim=8, ff=None):
 class Pair:
     """The library's handle and the oracle on the same random checkpoint."""
 
-    def __init__(self, cfg, seed=0, exact=True, max_ctx=1024, max_seqs=4, step_tokens=512, boost=None, plain=False):
+    def __init__(self, cfg, seed=0, exact=True, max_ctx=1024, max_seqs=4, step_tokens=512, boost=None, plain=False, edit=None):
         self.cfg = cfg
         w = synth.make_malasun(cfg, seed)
         f = {k: synth.bf16_to_f32(v) for k, v in w.items()}
@@ -40,6 +40,12 @@ class Pair:
             f["embed"] = f["embed"].copy()
             f["embed"][boost] *= 8.0
             w["embed"] = synth._bf16_round(f["embed"])
+        if edit is not None:        # edit(name, values) -> new values or None, for every tensor
+            for k in list(f):
+                a = edit(k, f[k])
+                if a is not None:
+                    w[k] = synth._bf16_round(np.asarray(a, np.float32))
+                    f[k] = synth.bf16_to_f32(w[k])
         self.m = B200Model("malasun", cfg, w, max_ctx=max_ctx, max_prefill=step_tokens, max_seqs=max_seqs, exact_fp32=exact, attn_impl=1 if plain else 0)
         self.o = Malasun(cfg, f)
         self.tol = TOL32 if exact else TOL16
@@ -176,6 +182,44 @@ def test_recurrence_sizes_beyond_one_column_slice():
         want = p.o.forward(ids)
         p.check(p.run_cuts(ids, [33, 34, 66] + list(range(67, 75))), want, "recurrence sizes")
         p.close()
+
+
+def test_long_portions_are_scanned_in_segments():
+    # Entries of 256 tokens and more are cut into 64-token segments that are scanned side by side and joined afterwards.  Forget gates
+    # held at 63/64 and above keep hundreds of tokens in the state, so a segment that started from the wrong state would show.  Sizes
+    # that are no multiples of the kernels' tiles; long entries that start a sequence and that continue one, beside short ones.
+    layers = [R(heads=2, dim=72, vdim=40), R(heads=3, dim=8, vdim=8, ff=24), A(heads=2, kv_heads=1, dim=16, vdim=16, window=48, conv=3), R(heads=1, dim=130, vdim=33)]
+    slow = lambda k, a: np.full_like(a, 0.984375) if k.endswith("mix.lower") else None
+    p = Pair(synth.malasun_config(layers, width=40, vocab=60), seed=23, max_ctx=2048, max_seqs=3, step_tokens=1024, edit=slow)
+    reqs = [p.ids(n, 30 + i) for i, n in enumerate([700, 530, 330])]
+    want = [p.o.forward(r) for r in reqs]
+    slots = [p.m.seq_open() for _ in reqs]
+    at, got = [0] * 3, [[] for _ in reqs]
+    plan = [[300, 0, 0], [257, 5, 1], [1, 260, 64], [100, 264, 256], [42, 1, 9]]
+    for step in plan:
+        ent, who = [], []
+        for i, n in enumerate(step):
+            if n > 0:
+                ent.append((slots[i], reqs[i][at[i]:at[i] + n], range(n))); who.append((i, n)); at[i] += n
+        lg = p.m.feed(ent)
+        r = 0
+        for i, n in who:
+            got[i].append(lg[r:r + n]); r += n
+    for i in range(3):
+        assert at[i] == len(reqs[i])
+        p.check(np.concatenate(got[i]), want[i], f"request {i} with segmented portions")
+    p.close()
+    # many heads x columns make the engine choose longer segments (128 tokens for the first prompt, 256 for the second)
+    p = Pair(synth.malasun_config([R(heads=8, dim=4, vdim=1184)], width=16, vocab=40), seed=25, max_ctx=2048, max_seqs=2, step_tokens=1100, edit=slow)
+    for n, cuts in ((700, [690]), (1060, [30])):
+        ids = p.ids(n, n)
+        p.check(p.run_cuts(ids, cuts), p.o.forward(ids), f"{n}-token prompt, longer segments")
+    p.close()
+    # serving mode (bf16 products), one long prompt against its own token-by-token tail
+    p = Pair(synth.malasun_config(layers, width=64, vocab=60), seed=24, exact=False, max_ctx=1024, step_tokens=1024, edit=slow)
+    ids = p.ids(600, 5)
+    p.check(p.run_cuts(ids, [590] + list(range(591, 600))), p.o.forward(ids), "segmented portion in serving mode")
+    p.close()
 
 
 def test_launches_shorter_than_a_step_are_cut_by_the_scheduler():
