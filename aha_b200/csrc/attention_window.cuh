@@ -140,7 +140,7 @@ struct WindowAttnArgs {
 
 constexpr int kWinAttnThreads = 128;
 constexpr int kWinAttnMaxAcc = 4;    // Dv <= 4 * 128
-constexpr int kWinSplitMaxTokens = 32, kWinMaxSplits = 32;
+constexpr int kWinSplitMaxTokens = 32, kWinMaxSplits = 32, kWinSplitKeys = 64;
 
 // One block per (token, head[, chunk of keys]).  Scores: a warp takes four keys at a time, its lanes run over the head dimension (one
 // coalesced read of each key row), so a tile of 128 keys costs 8 rounds per warp; softmax over the tile across the block; values: thread
@@ -152,6 +152,7 @@ static __global__ void __launch_bounds__(kWinAttnThreads) window_attn_kernel(Win
     float* qs = sm;                 // [D]
     float* sc = sm + D;             // [threads]
     float* red = sc + kWinAttnThreads;   // [32]
+    __shared__ int pgs[kWinAttnThreads / kPage + 1];      // physical pages of the tile's keys
     const int t = blockIdx.x, h = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = h / (a.H / a.kv.G);
     const int e = a.rb.tok_entry[t], i = a.rb.tok_pos[t], slot = a.rb.ent_slot[e];
@@ -173,14 +174,16 @@ static __global__ void __launch_bounds__(kWinAttnThreads) window_attn_kernel(Win
 #pragma unroll
     for (int r = 0; r < kWinAttnMaxAcc; ++r) acc[r] = 0.f;
     for (int jt = ja; jt < jb; jt += kWinAttnThreads) {
-        const int nj = min(kWinAttnThreads, jb - jt);
+        const int nj = min(kWinAttnThreads, jb - jt), pg0 = jt >> kPageShift;
+        if (tid <= ((jt + nj - 1) >> kPageShift) - pg0) pgs[tid] = pt[pg0 + tid];
+        __syncthreads();
         for (int k0 = warp * 4; k0 < nj; k0 += 16) {
             const float* kr[4];
             float dot[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
             for (int u = 0; u < 4; ++u) {
                 const int j = jt + min(k0 + u, nj - 1);
-                kr[u] = a.kv.k_row(pt[j >> kPageShift], g, j & (kPage - 1));
+                kr[u] = a.kv.k_row(pgs[(j >> kPageShift) - pg0], g, j & (kPage - 1));
             }
             for (int d = lane; d < D; d += 32) {
                 const float qd = qs[d];
@@ -207,10 +210,10 @@ static __global__ void __launch_bounds__(kWinAttnThreads) window_attn_kernel(Win
             const int c = tid + r * kWinAttnThreads;
             if (c < Dv) {
                 float o = acc[r] * corr;
-#pragma unroll 4
+#pragma unroll 8
                 for (int jj = 0; jj < nj; ++jj) {
                     const int jk = jt + jj;
-                    o = fmaf(sc[jj], a.kv.v_row(pt[jk >> kPageShift], g, jk & (kPage - 1))[c], o);
+                    o = fmaf(sc[jj], a.kv.v_row(pgs[(jk >> kPageShift) - pg0], g, jk & (kPage - 1))[c], o);
                 }
                 acc[r] = o;
             }
@@ -276,8 +279,8 @@ inline int window_attn(cudaStream_t st, WindowAttnArgs a, int kv_span) {
     AHA_REQUIRE(a.kv.Dv <= kWinAttnMaxAcc * kWinAttnThreads, "window attention: value head size above 512");
     const size_t smem = ((size_t)a.kv.D + kWinAttnThreads + 32) * sizeof(float);
     if (a.part && a.rb.T <= kWinSplitMaxTokens && kv_span > kWinAttnThreads) {
-        a.nsplit = std::min(kWinMaxSplits, ceil_div(kv_span, kWinAttnThreads));
-        a.chunk = ceil_div(ceil_div(kv_span, a.nsplit), kWinAttnThreads) * kWinAttnThreads;
+        a.nsplit = std::min(kWinMaxSplits, ceil_div(kv_span, kWinSplitKeys));      // short chunks: a block walks its keys in order
+        a.chunk = ceil_div(ceil_div(kv_span, a.nsplit), kPage) * kPage;
         a.skip_from_n = 0;
         window_attn_kernel<true><<<dim3(a.rb.T, a.H, a.nsplit), kWinAttnThreads, smem, st>>>(a);
         window_attn_merge_kernel<<<dim3(a.rb.T, a.H), kWinAttnThreads, 0, st>>>(a);
