@@ -111,6 +111,7 @@ static __global__ void __launch_bounds__(256) gemm_skinny_kernel(GemmAnyArgs g) 
 #pragma unroll
         for (int r = 0; r < MB; ++r) { acc0[r] = 0.f; acc1[r] = 0.f; }
         if (VEC) {
+#pragma unroll 4      // four steps' weight loads (eight of 16 bytes per lane) in flight: a warp's two rows alone do not cover the memory latency
             for (int k = lane * 8; k < g.K; k += 256) {
                 float a[8], b[8];
                 load_w8(w0 + k, a);

@@ -306,7 +306,7 @@ static __global__ void __launch_bounds__(256) hgrn2_out_norm_kernel(float* __res
 //   hgrn2_scan_reg_kernel       every segment from zero: local outputs, the segment's local end state into scratch
 //   hgrn2_seg_decay_kernel      q_t <- A_t * q_t in place (segments after an entry's first), the segment's whole product into scratch
 //   hgrn2_seg_combine_kernel    walks an entry's segments in order: scratch <- the state BEFORE the segment, slot <- the end state
-//   hgrn2_seg_apply_kernel      out_t += S0^T (A_t * q_t), fp32 on the CUDA cores, a (64 tokens x 32 columns) tile per block
+//   hgrn2_seg_apply_kernel      out_t += S0^T (A_t * q_t), fp32 on the CUDA cores, a (64 tokens x 64 columns) tile per block
 constexpr int kSegLen = 64;         // the shortest segment; segments are a power-of-two multiple of it (and so of kScanChunk)
 constexpr int kSegLenMax = 256;
 constexpr int kSegMinEntry = 256;   // a step whose longest entry has fewer tokens walks its entries whole
@@ -347,34 +347,34 @@ static __global__ void hgrn2_seg_combine_kernel(Hgrn2Args a) {
 }
 
 static __global__ void __launch_bounds__(256) hgrn2_seg_apply_kernel(Hgrn2Args a) {
-    __shared__ float Ss[64][32];
+    __shared__ float Ss[64][64];
     __shared__ __align__(16) float Qs[64][64];
     const int e = blockIdx.x / a.seg_max, k = blockIdx.x % a.seg_max, h = blockIdx.y;
     if (k == 0 || k >= hgrn2_seg_count(a.rb, e, a.seg_len)) return;
-    const int D = a.D, Dv = a.Dv, tid = threadIdx.x, tg = tid >> 5, jl = tid & 31, j = blockIdx.z * 32 + jl;
+    const int D = a.D, Dv = a.Dv, tid = threadIdx.x, tg = tid >> 5, jl = tid & 31, jb = blockIdx.z * 64;
     const int t0 = a.rb.ent_start[e] + k * a.seg_len, t1 = min(a.rb.ent_start[e + 1], t0 + a.seg_len);
     const float* S0 = a.seg_state + ((size_t)(hgrn2_seg_base(a.rb, e, a.seg_len) + k) * a.H + h) * D * Dv;
     for (int tt = t0; tt < t1; tt += 64) {
-        float acc[8];
+        float acc[8][2];       // tokens tg * 8 .. + 7, columns jl and jl + 32 of the block's 64
 #pragma unroll
-        for (int u = 0; u < 8; ++u) acc[u] = 0.f;
+        for (int u = 0; u < 8; ++u) acc[u][0] = acc[u][1] = 0.f;
         for (int i0 = 0; i0 < D; i0 += 64) {
-            for (int idx = tid; idx < 64 * 32; idx += 256) {
-                const int ii = idx >> 5, jc = blockIdx.z * 32 + (idx & 31);
-                Ss[ii][idx & 31] = (i0 + ii < D && jc < Dv) ? S0[(size_t)(i0 + ii) * Dv + jc] : 0.f;
-            }
             for (int idx = tid; idx < 64 * 64; idx += 256) {
-                const int tl = idx >> 6, ii = idx & 63;
-                Qs[tl][ii] = (tt + tl < t1 && i0 + ii < D) ? a.qfv[(size_t)(tt + tl) * a.ld + h * D + i0 + ii] : 0.f;
+                const int ii = idx >> 6, jc = idx & 63;
+                Ss[ii][jc] = (i0 + ii < D && jb + jc < Dv) ? S0[(size_t)(i0 + ii) * Dv + jb + jc] : 0.f;
+                Qs[ii][jc] = (tt + ii < t1 && i0 + jc < D) ? a.qfv[(size_t)(tt + ii) * a.ld + h * D + i0 + jc] : 0.f;     // here ii is a token, jc a state row
             }
             __syncthreads();
-#pragma unroll 4
+#pragma unroll 2
             for (int ii = 0; ii < 64; ii += 4) {
-                const float s0 = Ss[ii][jl], s1 = Ss[ii + 1][jl], s2 = Ss[ii + 2][jl], s3 = Ss[ii + 3][jl];
+                float s0[4], s1[4];
+#pragma unroll
+                for (int v = 0; v < 4; ++v) { s0[v] = Ss[ii + v][jl]; s1[v] = Ss[ii + v][jl + 32]; }
 #pragma unroll
                 for (int u = 0; u < 8; ++u) {
                     const float4 q = *reinterpret_cast<const float4*>(&Qs[tg * 8 + u][ii]);
-                    acc[u] = fmaf(s3, q.w, fmaf(s2, q.z, fmaf(s1, q.y, fmaf(s0, q.x, acc[u]))));
+                    acc[u][0] = fmaf(s0[3], q.w, fmaf(s0[2], q.z, fmaf(s0[1], q.y, fmaf(s0[0], q.x, acc[u][0]))));
+                    acc[u][1] = fmaf(s1[3], q.w, fmaf(s1[2], q.z, fmaf(s1[1], q.y, fmaf(s1[0], q.x, acc[u][1]))));
                 }
             }
             __syncthreads();
@@ -382,7 +382,11 @@ static __global__ void __launch_bounds__(256) hgrn2_seg_apply_kernel(Hgrn2Args a
 #pragma unroll
         for (int u = 0; u < 8; ++u) {
             const int t = tt + tg * 8 + u;
-            if (t < t1 && j < Dv) a.out[(size_t)t * a.H * Dv + h * Dv + j] += acc[u];
+            if (t < t1) {
+                float* o = a.out + (size_t)t * a.H * Dv + h * Dv + jb + jl;
+                if (jb + jl < Dv) o[0] += acc[u][0];
+                if (jb + jl + 32 < Dv) o[32] += acc[u][1];
+            }
         }
     }
 }
@@ -421,7 +425,7 @@ inline int hgrn2_scan(cudaStream_t st, const Hgrn2Args& a, int impl = 0) {
         hgrn2_seg_decay_kernel<<<dim3(segs, a.H), ((a.D + 31) / 32) * 32, 0, st>>>(a);
         const size_t n = (size_t)a.H * a.D * a.Dv;
         hgrn2_seg_combine_kernel<<<dim3((unsigned)((n + 255) / 256), a.rb.E), 256, 0, st>>>(a);
-        hgrn2_seg_apply_kernel<<<dim3(segs, a.H, (a.Dv + 31) / 32), 256, 0, st>>>(a);
+        hgrn2_seg_apply_kernel<<<dim3(segs, a.H, (a.Dv + 63) / 64), 256, 0, st>>>(a);
     }
     hgrn2_out_norm_kernel<<<(unsigned)(((size_t)T * a.H * 32 + 255) / 256), 256, 0, st>>>(a.out, a.norm_w, a.eps, T * a.H, a.Dv);
     AHA_CUDA_CHECK(cudaGetLastError());

@@ -572,10 +572,10 @@ struct Hgrn2Mixer final : Sublayer {
         int longest = 0;
         for (int e = 0; e < v.rb.E; ++e) longest = std::max(longest, v.h_ent_start[e + 1] - v.h_ent_start[e]);
         if (longest >= kSegMinEntry && E.seg_state && E.opt.seq_impl == 0) {      // long prompt portions: segments scanned side by side
-            // the shortest segments that still give every SM several blocks: a segment costs a pass over the head's state
+            // the longest segments that still give every SM four blocks: every segment costs a pass over the head's state
             const int per_seg = H * ((Dv + kScanCols - 1) / kScanCols);
             int L = kSegLen;
-            while (L < kSegLenMax && (longest / (2 * L)) * per_seg >= 8 * E.c.num_sms) L *= 2;
+            while (L < kSegLenMax && (longest / (2 * L)) * per_seg >= 4 * E.c.num_sms) L *= 2;
             if (longest > L) { a.seg_state = E.seg_state; a.seg_decay = E.seg_decay; a.seg_len = L; a.seg_max = (longest + L - 1) / L; }
         }
         E.tic("hgrn2 recurrence", 4.0 * T * H * D * Dv, 4.0 * T * (in.N + H * Dv) + 8.0 * v.rb.E * slot_stride);

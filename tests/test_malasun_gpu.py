@@ -211,7 +211,7 @@ def test_long_portions_are_scanned_in_segments():
     p.close()
     # many heads x columns make the engine choose longer segments (128 tokens for the first prompt, 256 for the second)
     p = Pair(synth.malasun_config([R(heads=8, dim=4, vdim=1184)], width=16, vocab=40), seed=25, max_ctx=2048, max_seqs=2, step_tokens=1100, edit=slow)
-    for n, cuts in ((700, [690]), (1060, [30])):
+    for n, cuts in ((500, [490]), (1060, [30])):
         ids = p.ids(n, n)
         p.check(p.run_cuts(ids, cuts), p.o.forward(ids), f"{n}-token prompt, longer segments")
     p.close()
