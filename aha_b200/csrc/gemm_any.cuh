@@ -2,8 +2,9 @@
 // fp32 or bf16.  Every product and every sum is fp32 (a bf16 weight widens exactly), so with fp32 weights this is the "true
 // 32-bit" path of a model, and with bf16 weights it is the exact twin of the tensor-core path.  Two kernels:
 //   gemm_any_kernel     64 x 64 tiles, bounds-checked on every side (sizes come from a checkpoint's config, nothing is assumed)
-//   gemm_skinny_kernel  M <= 8 rows (decode steps): one warp per output column streams that weight row once for all rows
-// Both accumulate a given output element in an order that depends only on (K, kernel), never on M or on the other rows.
+//   gemm_skinny_kernel  M <= 2 rows (decode steps), or rows that cannot be read 16 bytes at a time: a warp streams two weight rows once for all rows
+//   gemm_rows_kernel    3 <= M <= 8 rows (decode steps of several sequences): a block owns 8 columns, its warps split K, activations in registers
+// Each accumulates a given output element in an order that depends only on (K, kernel), never on the other rows' values.
 #pragma once
 #include <cuda_bf16.h>
 
@@ -145,6 +146,59 @@ static __global__ void __launch_bounds__(256) gemm_skinny_kernel(GemmAnyArgs g) 
     }
 }
 
+// 3 <= M <= MB rows, K % 8 == 0, 16-byte aligned rows.  A block owns 8 output columns; its 8 warps take the steps of 256 elements of K in
+// turn (lane l: elements 8 l .. 8 l + 7 of a step).  A lane keeps the activations of its step for all rows in registers and multiplies them
+// with its 8 elements of each of the 8 weight rows: an activation is read once per 8 columns (the two-column kernel reads it again for
+// every pair of columns and, with 8 rows, spends its time waiting for those loads), and all 8 weight loads of a step are in flight together.
+// The partial sums are tree-summed in the warp, then over the warps in a fixed order.
+template <typename WT, int EPI, int MB>
+static __global__ void __launch_bounds__(256) gemm_rows_kernel(GemmAnyArgs g) {
+    constexpr int NC = 8;
+    __shared__ float part[8][NC * MB];
+    const WT* __restrict__ W = reinterpret_cast<const WT*>(g.W);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n0 = blockIdx.x * NC;
+    float acc[NC][MB];
+#pragma unroll
+    for (int c = 0; c < NC; ++c)
+#pragma unroll
+        for (int r = 0; r < MB; ++r) acc[c][r] = 0.f;
+    for (int k = warp * 256 + lane * 8; k < g.K; k += 8 * 256) {
+        float w[NC][8], x[MB][8];
+#pragma unroll
+        for (int c = 0; c < NC; ++c) load_w8(W + (size_t)min(n0 + c, g.N - 1) * g.K + k, w[c]);
+#pragma unroll
+        for (int r = 0; r < MB; ++r) {
+            float4 x0 = make_float4(0.f, 0.f, 0.f, 0.f), x1 = x0;
+            if (r < g.M) {
+                x0 = *reinterpret_cast<const float4*>(g.A + (size_t)r * g.lda + k);
+                x1 = *reinterpret_cast<const float4*>(g.A + (size_t)r * g.lda + k + 4);
+            }
+            x[r][0] = x0.x; x[r][1] = x0.y; x[r][2] = x0.z; x[r][3] = x0.w; x[r][4] = x1.x; x[r][5] = x1.y; x[r][6] = x1.z; x[r][7] = x1.w;
+        }
+#pragma unroll
+        for (int c = 0; c < NC; ++c)
+#pragma unroll
+            for (int r = 0; r < MB; ++r)
+#pragma unroll
+                for (int i = 0; i < 8; ++i) acc[c][r] = fmaf(x[r][i], w[c][i], acc[c][r]);
+    }
+#pragma unroll
+    for (int c = 0; c < NC; ++c)
+#pragma unroll
+        for (int r = 0; r < MB; ++r) {
+            const float v = warp_sum(acc[c][r]);
+            if (lane == 0) part[warp][c * MB + r] = v;
+        }
+    __syncthreads();
+    if (threadIdx.x < NC * MB) {
+        const int c = threadIdx.x / MB, r = threadIdx.x % MB, n = n0 + c;
+        float v = 0.f;
+#pragma unroll
+        for (int wp = 0; wp < 8; ++wp) v += part[wp][threadIdx.x];
+        if (r < g.M && n < g.N) g.C[(size_t)r * g.ldc + n] = any_epilogue<EPI>(g, v, n);
+    }
+}
+
 template <typename WT, int EPI, bool VEC>
 inline void gemm_skinny_launch(cudaStream_t st, const GemmAnyArgs& g, int num_sms) {
     const int blocks = std::max(1, std::min(ceil_div(g.N, 16), num_sms * 8));
@@ -158,7 +212,11 @@ template <typename WT, int EPI>
 inline void gemm_any_launch(cudaStream_t st, const GemmAnyArgs& g, int num_sms) {
     if (g.M <= 8) {
         const bool vec = g.K % 8 == 0 && g.lda % 4 == 0 && (reinterpret_cast<uintptr_t>(g.A) & 15) == 0 && (reinterpret_cast<uintptr_t>(g.W) & 15) == 0;
-        if (vec) gemm_skinny_launch<WT, EPI, true>(st, g, num_sms); else gemm_skinny_launch<WT, EPI, false>(st, g, num_sms);
+        if (vec && g.M >= 3) {
+            if (g.M <= 4) gemm_rows_kernel<WT, EPI, 4><<<ceil_div(g.N, 8), 256, 0, st>>>(g);
+            else gemm_rows_kernel<WT, EPI, 8><<<ceil_div(g.N, 8), 256, 0, st>>>(g);
+        } else if (vec) gemm_skinny_launch<WT, EPI, true>(st, g, num_sms);
+        else gemm_skinny_launch<WT, EPI, false>(st, g, num_sms);
     } else {
         gemm_any_kernel<WT, EPI><<<dim3(ceil_div(g.N, 64), ceil_div(g.M, 64)), 256, 0, st>>>(g);
     }

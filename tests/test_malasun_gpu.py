@@ -115,7 +115,7 @@ def test_whole_model_portions_and_decoding(exact):
     ids = p.ids(150, 3)
     want = p.o.forward(ids)
     p.check(p.run_cuts(ids, []), want, "whole")
-    p.check(p.run_cuts(ids, [2, 4, 5, 31, 32, 33, 64, 96, 97, 127, 129]), want, "portions at page and window borders")
+    p.check(p.run_cuts(ids, [2, 4, 5, 8, 15, 31, 32, 33, 64, 96, 97, 127, 129]), want, "portions of 1, 2, 3, 7 and more tokens, at page and window borders")
     p.check(p.run_cuts(ids, list(range(60, 150))), want, "prompt then 90 decoded tokens (past every window)")
     p.check(p.run_cuts(ids, list(range(1, 12))), want, "the first tokens one by one")
     p.close()
