@@ -2,8 +2,8 @@
 // fp32 or bf16.  Every product and every sum is fp32 (a bf16 weight widens exactly), so with fp32 weights this is the "true
 // 32-bit" path of a model, and with bf16 weights it is the exact twin of the tensor-core path.  Two kernels:
 //   gemm_any_kernel     64 x 64 tiles, bounds-checked on every side (sizes come from a checkpoint's config, nothing is assumed)
-//   gemm_skinny_kernel  M <= 2 rows (decode steps), or rows that cannot be read 16 bytes at a time: a warp streams two weight rows once for all rows
-//   gemm_rows_kernel    3 <= M <= 8 rows (decode steps of several sequences): a block owns 8 columns, its warps split K, activations in registers
+//   gemm_rows_kernel    M <= 8 rows (decode steps): a block owns 8 columns, its warps split K, activations in registers
+//   gemm_skinny_kernel  M <= 8 rows that cannot be read 16 bytes at a time, or one or two rows of a short K: a warp streams two weight rows
 // Each accumulates a given output element in an order that depends only on (K, kernel), never on the other rows' values.
 #pragma once
 #include <cuda_bf16.h>
@@ -146,7 +146,7 @@ static __global__ void __launch_bounds__(256) gemm_skinny_kernel(GemmAnyArgs g) 
     }
 }
 
-// 3 <= M <= MB rows, K % 8 == 0, 16-byte aligned rows.  A block owns 8 output columns; its 8 warps take the steps of 256 elements of K in
+// M <= MB rows, K % 8 == 0, 16-byte aligned rows.  A block owns 8 output columns; its 8 warps take the steps of 256 elements of K in
 // turn (lane l: elements 8 l .. 8 l + 7 of a step).  A lane keeps the activations of its step for all rows in registers and multiplies them
 // with its 8 elements of each of the 8 weight rows: an activation is read once per 8 columns (the two-column kernel reads it again for
 // every pair of columns and, with 8 rows, spends its time waiting for those loads), and all 8 weight loads of a step are in flight together.
@@ -162,6 +162,7 @@ static __global__ void __launch_bounds__(256) gemm_rows_kernel(GemmAnyArgs g) {
     for (int c = 0; c < NC; ++c)
 #pragma unroll
         for (int r = 0; r < MB; ++r) acc[c][r] = 0.f;
+#pragma unroll(MB <= 2 ? 4 : 1)      // few rows leave registers for several steps' loads in flight
     for (int k = warp * 256 + lane * 8; k < g.K; k += 8 * 256) {
         float w[NC][8], x[MB][8];
 #pragma unroll
@@ -212,8 +213,10 @@ template <typename WT, int EPI>
 inline void gemm_any_launch(cudaStream_t st, const GemmAnyArgs& g, int num_sms) {
     if (g.M <= 8) {
         const bool vec = g.K % 8 == 0 && g.lda % 4 == 0 && (reinterpret_cast<uintptr_t>(g.A) & 15) == 0 && (reinterpret_cast<uintptr_t>(g.W) & 15) == 0;
-        if (vec && g.M >= 3) {
-            if (g.M <= 4) gemm_rows_kernel<WT, EPI, 4><<<ceil_div(g.N, 8), 256, 0, st>>>(g);
+        if (vec && (g.M >= 3 || g.K >= 1024)) {      // one or two rows of a short K leave most of the 8 warps without a step: the two-column kernel
+            if (g.M <= 1) gemm_rows_kernel<WT, EPI, 1><<<ceil_div(g.N, 8), 256, 0, st>>>(g);
+            else if (g.M <= 2) gemm_rows_kernel<WT, EPI, 2><<<ceil_div(g.N, 8), 256, 0, st>>>(g);
+            else if (g.M <= 4) gemm_rows_kernel<WT, EPI, 4><<<ceil_div(g.N, 8), 256, 0, st>>>(g);
             else gemm_rows_kernel<WT, EPI, 8><<<ceil_div(g.N, 8), 256, 0, st>>>(g);
         } else if (vec) gemm_skinny_launch<WT, EPI, true>(st, g, num_sms);
         else gemm_skinny_launch<WT, EPI, false>(st, g, num_sms);
