@@ -47,7 +47,8 @@ __device__ __forceinline__ float conv_input(const QkvPrepArgs& a, int t, int loc
     return tail[(size_t)(a.taps - 1 + local - back) * ctot + coff + c];
 }
 
-static __global__ void __launch_bounds__(256) qkv_conv_norm_kernel(QkvPrepArgs a) {
+template <int THREADS>
+static __global__ void __launch_bounds__(THREADS) qkv_conv_norm_kernel(QkvPrepArgs a) {
     __shared__ float red[32];
     const int t = blockIdx.x;
     const int e = a.rb.tok_entry[t], pos = a.rb.tok_pos[t], local = t - a.rb.ent_start[e], slot = a.rb.ent_slot[e];
@@ -263,7 +264,8 @@ static __global__ void __launch_bounds__(kWinAttnThreads) window_attn_merge_kern
 inline int qkv_prepare(cudaStream_t st, const QkvPrepArgs& a, bool only_single) {
     if (a.rb.T == 0) return 0;
     AHA_REQUIRE(a.taps <= kConvMaxTaps, "short convolution: more than 16 taps");
-    qkv_conv_norm_kernel<<<a.rb.T, 256, 0, st>>>(a);
+    if (a.rb.T <= 8) qkv_conv_norm_kernel<1024><<<a.rb.T, 1024, 0, st>>>(a);      // a decode step has few blocks: more threads for each
+    else qkv_conv_norm_kernel<256><<<a.rb.T, 256, 0, st>>>(a);
     const bool tail_launch = a.taps > 1 && !only_single;
     if (tail_launch) conv_tail_update_kernel<<<a.rb.E, 256, 0, st>>>(a);
     AHA_CUDA_CHECK(cudaGetLastError());

@@ -432,17 +432,18 @@ struct Engine final : SeqEngine {
         if (fp32) embed_gather_any_kernel<float><<<T, 128, 0, st>>>(rb.tokens, reinterpret_cast<const float*>(embed), x, W, V);
         else embed_gather_any_kernel<__nv_bfloat16><<<T, 128, 0, st>>>(rb.tokens, reinterpret_cast<const __nv_bfloat16*>(embed), x, W, V);
         c.cnt.kernels++;
+        const int norm_threads = T <= 8 ? std::min(1024, std::max(256, (W / 2 + 31) / 32 * 32)) : 256;      // a decode step has few blocks: more threads for each
         StepView v{this, rb, x, y, h_meta + 4 * Tmax, h_meta + 4 * Tmax + (slots + 1), h_meta + 4 * Tmax + (slots + 1) + slots, cur_span};
         for (int l = 0; l < L; ++l) {
             LayerRec& Ly = layers[l];
             Ly.mixer->run(v);
             tic("norm + residual", 4.0 * T * W, 12.0 * T * W);
-            scalar_rmsnorm_add_kernel<<<T, 256, 0, st>>>(x, y, Ly.gain1, eps, W); c.cnt.kernels++;
+            scalar_rmsnorm_add_kernel<<<T, norm_threads, 0, st>>>(x, y, Ly.gain1, eps, W); c.cnt.kernels++;
             toc();
             if (Ly.ff) {
                 Ly.ff->run(v);
                 tic("norm + residual", 4.0 * T * W, 12.0 * T * W);
-                scalar_rmsnorm_add_kernel<<<T, 256, 0, st>>>(x, y, Ly.gain2, eps, W); c.cnt.kernels++;
+                scalar_rmsnorm_add_kernel<<<T, norm_threads, 0, st>>>(x, y, Ly.gain2, eps, W); c.cnt.kernels++;
                 toc();
             }
             if (trace) AHA_CUDA_CHECK(cudaMemcpyAsync(trace_buf + (size_t)l * Tmax * W, x, (size_t)T * W * sizeof(float), cudaMemcpyDeviceToDevice, st));
