@@ -21,8 +21,9 @@ struct PagedKV {           // one layer's cache: K pages [page][G][kPage][D], V 
     float* k = nullptr;
     float* v = nullptr;
     int G = 0, D = 0, Dv = 0;
+    int ldv = 0;           // floats between value rows; 0: Dv.  With v = k and ldv = D the values are the first Dv columns of the key rows (one array holds both)
     __device__ __forceinline__ float* k_row(int page, int g, int tok_in_page) const { return k + (((size_t)page * G + g) * kPage + tok_in_page) * D; }
-    __device__ __forceinline__ float* v_row(int page, int g, int tok_in_page) const { return v + (((size_t)page * G + g) * kPage + tok_in_page) * Dv; }
+    __device__ __forceinline__ float* v_row(int page, int g, int tok_in_page) const { return v + (((size_t)page * G + g) * kPage + tok_in_page) * (ldv ? ldv : Dv); }
 };
 
 struct QkvPrepArgs {

@@ -12,7 +12,7 @@
 
 namespace aha {
 
-enum AnyEpi { AEPI_STORE = 0, AEPI_XIELU = 1 };
+enum AnyEpi { AEPI_STORE = 0, AEPI_XIELU = 1, AEPI_SWIGLU = 2 };   // SWIGLU: rows of W alternate gate / up; C[m][n / 2] = silu(gate) * up (N even)
 
 struct GemmAnyArgs {
     const float* A; int lda;
@@ -21,7 +21,35 @@ struct GemmAnyArgs {
     float* C; int ldc;
     int M, N, K;
     float act_a, act_b;       // AEPI_XIELU: alpha_p, alpha_n
+    // Batches (grid z).  Batch b reads A + ai * a_bs and W + wi * w_bs (bias + wi * N) and writes C + b * c_bs, ai = a_index ? a_index[b] : b,
+    // wi = w_index ? w_index[b] : b (both device arrays): per-head products (a_bs = the head's column offset), one expert's matrix per row, ...
+    int batch = 1;
+    size_t a_bs = 0, w_bs = 0, c_bs = 0;
+    const int* a_index = nullptr;
+    const int* w_index = nullptr;
+    // row_offsets (device, [batch + 1]): batch b owns rows [ro[b], ro[b + 1]) of A and C, M is an upper bound of a batch's rows (tile kernel only)
+    const int* row_offsets = nullptr;
+    const int* a_gather = nullptr;   // (tile kernel only) row m of A is row a_gather[m] of the buffer: a gather folded into the load
 };
+
+// the block's batch: advances A, C, bias (and the returned W) and, with row offsets, narrows M
+template <typename WT>
+__device__ __forceinline__ const WT* any_batch_setup(GemmAnyArgs& g) {
+    const WT* W = reinterpret_cast<const WT*>(g.W);
+    const int b = blockIdx.z;
+    const int wi = g.w_index ? g.w_index[b] : b;
+    W += (size_t)wi * g.w_bs;
+    if (g.bias) g.bias += (size_t)wi * (g.w_bs ? g.N : 0);
+    g.A += (size_t)(g.a_index ? g.a_index[b] : b) * g.a_bs;
+    g.C += (size_t)b * g.c_bs;
+    if (g.row_offsets) {
+        const int r0 = g.row_offsets[b];
+        g.M = g.row_offsets[b + 1] - r0;
+        if (g.a_gather) g.a_gather += r0; else g.A += (size_t)r0 * g.lda;
+        g.C += (size_t)r0 * g.ldc;
+    }
+    return W;
+}
 
 __device__ __forceinline__ float wt_to_f(float v) { return v; }
 __device__ __forceinline__ float wt_to_f(__nv_bfloat16 v) { return __bfloat162float(v); }
@@ -33,14 +61,20 @@ __device__ __forceinline__ float any_epilogue(const GemmAnyArgs& g, float v, int
     return v;
 }
 
+__device__ __forceinline__ float any_swiglu(const GemmAnyArgs& g, float gate, float up, int n) {
+    if (g.bias) { gate += g.bias[n]; up += g.bias[n + 1]; }
+    return silu_f(gate) * up;
+}
+
 template <typename WT, int EPI>
 static __global__ void __launch_bounds__(256) gemm_any_kernel(GemmAnyArgs g) {
     constexpr int BM = 64, BN = 64, BK = 16, PAD = 4;
     __shared__ __align__(16) float As[BK][BM + PAD];
     __shared__ __align__(16) float Bs[BK][BN + PAD];
-    const WT* __restrict__ W = reinterpret_cast<const WT*>(g.W);
+    const WT* __restrict__ W = any_batch_setup<WT>(g);
     const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
     const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+    if (m0 >= g.M) return;
     const int lr = tid >> 2, lk = (tid & 3) * 4;
     float acc[4][4];
 #pragma unroll
@@ -48,12 +82,13 @@ static __global__ void __launch_bounds__(256) gemm_any_kernel(GemmAnyArgs g) {
 #pragma unroll
         for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
     const int m = m0 + lr, n = n0 + lr;
+    const float* arow = g.A + (size_t)((g.a_gather && m < g.M) ? g.a_gather[m] : m) * g.lda;
     for (int k0 = 0; k0 < g.K; k0 += BK) {
         float a[4], b[4];
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             const int kk = k0 + lk + i;
-            a[i] = (m < g.M && kk < g.K) ? g.A[(size_t)m * g.lda + kk] : 0.f;
+            a[i] = (m < g.M && kk < g.K) ? arow[kk] : 0.f;
             b[i] = (n < g.N && kk < g.K) ? wt_to_f(W[(size_t)n * g.K + kk]) : 0.f;
         }
         __syncthreads();
@@ -75,6 +110,14 @@ static __global__ void __launch_bounds__(256) gemm_any_kernel(GemmAnyArgs g) {
     for (int i = 0; i < 4; ++i) {
         const int mm = m0 + ty * 4 + i;
         if (mm >= g.M) continue;
+        if (EPI == AEPI_SWIGLU) {
+#pragma unroll
+            for (int j = 0; j < 4; j += 2) {
+                const int nn = n0 + tx * 4 + j;
+                if (nn + 1 < g.N) g.C[(size_t)mm * g.ldc + nn / 2] = any_swiglu(g, acc[i][j], acc[i][j + 1], nn);
+            }
+            continue;
+        }
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             const int nn = n0 + tx * 4 + j;
@@ -101,7 +144,7 @@ __device__ __forceinline__ void load_w8(const float* p, float (&w)[8]) {
 // launch with 16-byte loads (VEC: K % 8 == 0 and 16-byte aligned rows; otherwise element by element).
 template <typename WT, int EPI, int MB, bool VEC>
 static __global__ void __launch_bounds__(256) gemm_skinny_kernel(GemmAnyArgs g) {
-    const WT* __restrict__ W = reinterpret_cast<const WT*>(g.W);
+    const WT* __restrict__ W = any_batch_setup<WT>(g);
     const int lane = threadIdx.x & 31;
     const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, nwarps = (gridDim.x * blockDim.x) >> 5;
     for (int n = warp * 2; n < g.N; n += nwarps * 2) {
@@ -138,7 +181,9 @@ static __global__ void __launch_bounds__(256) gemm_skinny_kernel(GemmAnyArgs g) 
 #pragma unroll
         for (int r = 0; r < MB; ++r) {
             const float v0 = warp_sum(acc0[r]), v1 = warp_sum(acc1[r]);
-            if (lane == 0 && r < g.M) {
+            if (EPI == AEPI_SWIGLU) {
+                if (lane == 0 && r < g.M && two) g.C[(size_t)r * g.ldc + n / 2] = any_swiglu(g, v0, v1, n);
+            } else if (lane == 0 && r < g.M) {
                 g.C[(size_t)r * g.ldc + n] = any_epilogue<EPI>(g, v0, n);
                 if (two) g.C[(size_t)r * g.ldc + n + 1] = any_epilogue<EPI>(g, v1, n + 1);
             }
@@ -155,7 +200,7 @@ template <typename WT, int EPI, int MB>
 static __global__ void __launch_bounds__(256) gemm_rows_kernel(GemmAnyArgs g) {
     constexpr int NC = 8;
     __shared__ float part[8][NC * MB];
-    const WT* __restrict__ W = reinterpret_cast<const WT*>(g.W);
+    const WT* __restrict__ W = any_batch_setup<WT>(g);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n0 = blockIdx.x * NC;
     float acc[NC][MB];
 #pragma unroll
@@ -196,13 +241,20 @@ static __global__ void __launch_bounds__(256) gemm_rows_kernel(GemmAnyArgs g) {
         float v = 0.f;
 #pragma unroll
         for (int wp = 0; wp < 8; ++wp) v += part[wp][threadIdx.x];
-        if (r < g.M && n < g.N) g.C[(size_t)r * g.ldc + n] = any_epilogue<EPI>(g, v, n);
+        if (EPI == AEPI_SWIGLU) {      // the thread of an even column also sums its odd neighbour (the up projection)
+            if ((c & 1) == 0 && r < g.M && n + 1 < g.N) {
+                float u = 0.f;
+#pragma unroll
+                for (int wp = 0; wp < 8; ++wp) u += part[wp][threadIdx.x + MB];
+                g.C[(size_t)r * g.ldc + n / 2] = any_swiglu(g, v, u, n);
+            }
+        } else if (r < g.M && n < g.N) g.C[(size_t)r * g.ldc + n] = any_epilogue<EPI>(g, v, n);
     }
 }
 
 template <typename WT, int EPI, bool VEC>
 inline void gemm_skinny_launch(cudaStream_t st, const GemmAnyArgs& g, int num_sms) {
-    const int blocks = std::max(1, std::min(ceil_div(g.N, 16), num_sms * 8));
+    const dim3 blocks(std::max(1, std::min(ceil_div(g.N, 16), num_sms * 8)), 1, g.batch);
     if (g.M <= 1) gemm_skinny_kernel<WT, EPI, 1, VEC><<<blocks, 256, 0, st>>>(g);
     else if (g.M <= 2) gemm_skinny_kernel<WT, EPI, 2, VEC><<<blocks, 256, 0, st>>>(g);
     else if (g.M <= 4) gemm_skinny_kernel<WT, EPI, 4, VEC><<<blocks, 256, 0, st>>>(g);
@@ -211,28 +263,36 @@ inline void gemm_skinny_launch(cudaStream_t st, const GemmAnyArgs& g, int num_sm
 
 template <typename WT, int EPI>
 inline void gemm_any_launch(cudaStream_t st, const GemmAnyArgs& g, int num_sms) {
-    if (g.M <= 8) {
-        const bool vec = g.K % 8 == 0 && g.lda % 4 == 0 && (reinterpret_cast<uintptr_t>(g.A) & 15) == 0 && (reinterpret_cast<uintptr_t>(g.W) & 15) == 0;
+    if (g.M <= 8 && !g.row_offsets && !g.a_gather) {
+        const bool vec = g.K % 8 == 0 && g.lda % 4 == 0 && (reinterpret_cast<uintptr_t>(g.A) & 15) == 0 && (reinterpret_cast<uintptr_t>(g.W) & 15) == 0 &&
+                         (g.batch == 1 || (g.a_bs % 4 == 0 && g.w_bs % 8 == 0));
+        const dim3 grid(ceil_div(g.N, 8), 1, g.batch);
         if (vec && (g.M >= 3 || g.K >= 1024)) {      // one or two rows of a short K leave most of the 8 warps without a step: the two-column kernel
-            if (g.M <= 1) gemm_rows_kernel<WT, EPI, 1><<<ceil_div(g.N, 8), 256, 0, st>>>(g);
-            else if (g.M <= 2) gemm_rows_kernel<WT, EPI, 2><<<ceil_div(g.N, 8), 256, 0, st>>>(g);
-            else if (g.M <= 4) gemm_rows_kernel<WT, EPI, 4><<<ceil_div(g.N, 8), 256, 0, st>>>(g);
-            else gemm_rows_kernel<WT, EPI, 8><<<ceil_div(g.N, 8), 256, 0, st>>>(g);
+            if (g.M <= 1) gemm_rows_kernel<WT, EPI, 1><<<grid, 256, 0, st>>>(g);
+            else if (g.M <= 2) gemm_rows_kernel<WT, EPI, 2><<<grid, 256, 0, st>>>(g);
+            else if (g.M <= 4) gemm_rows_kernel<WT, EPI, 4><<<grid, 256, 0, st>>>(g);
+            else gemm_rows_kernel<WT, EPI, 8><<<grid, 256, 0, st>>>(g);
         } else if (vec) gemm_skinny_launch<WT, EPI, true>(st, g, num_sms);
         else gemm_skinny_launch<WT, EPI, false>(st, g, num_sms);
     } else {
-        gemm_any_kernel<WT, EPI><<<dim3(ceil_div(g.N, 64), ceil_div(g.M, 64)), 256, 0, st>>>(g);
+        gemm_any_kernel<WT, EPI><<<dim3(ceil_div(g.N, 64), ceil_div(g.M, 64), g.batch), 256, 0, st>>>(g);
     }
 }
 
 // fp32_weights: W holds floats, else bf16
 inline void gemm_any(cudaStream_t st, int epi, bool fp32_weights, const GemmAnyArgs& g, int num_sms) {
     if (g.M == 0 || g.N == 0) return;
-    AHA_REQUIRE(epi == AEPI_STORE || epi == AEPI_XIELU, "gemm_any: bad epilogue");
+    AHA_REQUIRE(epi == AEPI_STORE || epi == AEPI_XIELU || epi == AEPI_SWIGLU, "gemm_any: bad epilogue");
+    AHA_REQUIRE(epi != AEPI_SWIGLU || g.N % 2 == 0, "gemm_any: the gate / up epilogue needs an even number of weight rows");
+    AHA_REQUIRE(g.batch >= 1 && g.batch <= 65535, "gemm_any: bad batch count");
     if (fp32_weights) {
-        if (epi == AEPI_STORE) gemm_any_launch<float, AEPI_STORE>(st, g, num_sms); else gemm_any_launch<float, AEPI_XIELU>(st, g, num_sms);
+        if (epi == AEPI_STORE) gemm_any_launch<float, AEPI_STORE>(st, g, num_sms);
+        else if (epi == AEPI_XIELU) gemm_any_launch<float, AEPI_XIELU>(st, g, num_sms);
+        else gemm_any_launch<float, AEPI_SWIGLU>(st, g, num_sms);
     } else {
-        if (epi == AEPI_STORE) gemm_any_launch<__nv_bfloat16, AEPI_STORE>(st, g, num_sms); else gemm_any_launch<__nv_bfloat16, AEPI_XIELU>(st, g, num_sms);
+        if (epi == AEPI_STORE) gemm_any_launch<__nv_bfloat16, AEPI_STORE>(st, g, num_sms);
+        else if (epi == AEPI_XIELU) gemm_any_launch<__nv_bfloat16, AEPI_XIELU>(st, g, num_sms);
+        else gemm_any_launch<__nv_bfloat16, AEPI_SWIGLU>(st, g, num_sms);
     }
     AHA_CUDA_CHECK(cudaGetLastError());
 }

@@ -189,12 +189,12 @@ static __global__ void argmax_final_kernel(const float* __restrict__ pmax, const
 // ---- kernels of the ragged (varlen) path -------------------------------------------------------------------------------------------
 // Row gather from an embedding table stored as fp32 or bf16 (both widen exactly to the fp32 residual stream).
 template <typename WT>
-static __global__ void embed_gather_any_kernel(const uint32_t* __restrict__ ids, const WT* __restrict__ table, float* __restrict__ out, int H, int V) {
+static __global__ void embed_gather_any_kernel(const uint32_t* __restrict__ ids, const WT* __restrict__ table, float* __restrict__ out, int H, int V, float scale = 1.f) {
     const int s = blockIdx.x;
     uint32_t id = ids[s];
     if (id >= (uint32_t)V) id = V - 1;  // the host validates; keep the kernel memory-safe regardless
     const WT* row = table + (size_t)id * H;
-    for (int i = threadIdx.x; i < H; i += blockDim.x) out[(size_t)s * H + i] = (float)row[i];
+    for (int i = threadIdx.x; i < H; i += blockDim.x) out[(size_t)s * H + i] = (float)row[i] * scale;
 }
 
 // Post-norm residual step with a scalar gain: x[row] += g * y[row] / sqrt(mean(y[row]^2) + eps).  The gain is ONE number (read from

@@ -1,5 +1,10 @@
-// seq_engine.cu -- the layered sequence engine (see seq_engine.h): a model is a list of layers read from config.json,
-//     x += norm1(mixer(x));   x += norm2(ff(x))   (post-norms with a scalar gain; a layer may have no feed-forward)
+// seq_engine.cu -- the layered sequence engine (see seq_engine.h): a model is a list of layers read from config.json, each a mixer and
+// an optional feed-forward inside one of two layer templates (chosen by the config's "architecture"):
+//     post-norm   x += norm1(mixer(x));   x += norm2(ff(x))                      norms with ONE scalar gain on the sublayer outputs
+//     sandwich    x += m * norm1b(mixer(u)),  u = h + conv1(h),  h = norm1(x)    and the same around the feed-forward: RMS norms in groups with a
+//                 gain per channel before AND after each sublayer, a short causal convolution over time on what the sublayer reads (its last
+//                 inputs are state of the sequence), a residual multiplier m; a span of layers may run several times in a row with the same
+//                 weights ("loop"), every pass with a state of its own and a learned vector added to the stream before it
 // run by ONE ragged step function: the tokens of all entries of a step are packed into [T, width] fp32 rows, every Linear is one
 // GEMM over all rows, and the mixers' sequence kernels (recurrence.cuh, attention_window.cuh) take the RaggedBatch description.
 // Mixers and feed-forwards are looked up by name in a registry, each with its sizes and constants read from its config entry:
@@ -7,6 +12,10 @@
 //     "attention"  windowed softmax attention with a linear distance penalty, q/k/v bias, short convolution, whole-projection
 //                  q/k norm, sigmoid output gate, optional reuse of an earlier layer's cache     (attention_window.cuh)
 //     "dense"      W_down xIELU(W_up x)
+//     "gla"        gated linear attention: keyed diagonal recurrence, decay from a low-rank projection                (recurrence.cuh, ssm.cuh)
+//     "mamba2"     selective state space: convolved x / B / C, scalar decay per head, gate before a grouped norm        (recurrence.cuh, ssm.cuh)
+//     "latent_attention"  softmax attention over one cached latent + one rotated key part per token (YaRN rotary)       (attention_latent.cuh)
+//     "moe"        gated experts chosen by a table row of the token id, grouped matrix products                         (moe_table.cuh)
 // Memory: one free list of 32-token pages serves every layer that owns keys / values (K pages [page][G][32][D], V pages
 // [page][G][32][Dv], fp32); a sequence additionally owns a state slot (recurrent states, convolution tails, sampler state).
 // Precision: the residual stream, norms, gates, recurrent state, scores and softmax are fp32 in both modes; the Linear layers
@@ -17,15 +26,19 @@
 #include <functional>
 #include <memory>
 
+#include "attention_latent.cuh"
 #include "attention_tc.cuh"
 #include "attention_window.cuh"
 #include "gemm_any.cuh"
 #include "gemm_tc.cuh"
 #include "json.hpp"
 #include "kernels_common.cuh"
+#include "moe_table.cuh"
+#include "norm_group.cuh"
 #include "recurrence.cuh"
 #include "runtime.cuh"
 #include "sampling.cuh"
+#include "ssm.cuh"
 
 namespace aha {
 namespace {
@@ -68,6 +81,7 @@ struct Sublayer {
     virtual size_t seg_state_floats() const { return 0; }     // scratch of a recurrence that cuts long prompt portions into segments: states,
     virtual size_t seg_decay_floats() const { return 0; }     // ... and the segments' decay products
     virtual uint64_t kv_bytes_per_token() const { return 0; }
+    virtual size_t route_ints() const { return 0; }           // integer scratch of a routed feed-forward
 };
 
 struct Engine final : SeqEngine {
@@ -80,8 +94,32 @@ struct Engine final : SeqEngine {
     void* embed = nullptr;
     LinearAny head;
     float* final_gain = nullptr;
-    struct LayerRec { std::unique_ptr<Sublayer> mixer, ff; float *gain1 = nullptr, *gain2 = nullptr; };
+    // one RUN of a layer: a layer inside a loop appears once per pass, with the same weights and its own mixer object (state, cache)
+    struct LayerRec {
+        std::unique_ptr<Sublayer> mixer, ff;
+        float *gain1 = nullptr, *gain2 = nullptr;                   // post-norm template: scalar gains
+        float *pre1 = nullptr, *pre2 = nullptr, *post1 = nullptr, *post2 = nullptr;   // sandwich template: [W] gains before / after the sublayers
+        float *conv1 = nullptr, *conv2 = nullptr;                   // [W, taps] input convolutions
+        float *tails1 = nullptr, *tails2 = nullptr;                 // [slots][taps - 1][W] their state, per run
+        int pass = -1;                                              // >= 0: the run opens this pass of the loop (loop_step row added first)
+    };
     std::vector<LayerRec> layers;
+    bool sandwich = false;
+    int norm_groups = 1, conv_taps = 0;
+    float resid_mult = 1.f, embed_scale = 1.f, logit_scale = 1.f;
+    float* final_w = nullptr;      // sandwich: [W] gain of the final norm
+    float* loop_step = nullptr;    // [passes, W]
+    float *hnorm = nullptr, *hin = nullptr;   // [T, W] normed rows, sublayer input
+    int* route_buf = nullptr;
+    // weights that several runs share are loaded once
+    std::map<std::string, LinearAny> lin_cache;
+    std::map<std::string, float*> vec_cache;
+    std::map<std::string, int*> int_cache;
+    float* vec(const WeightTable& wt, const std::string& name, size_t n) {
+        auto it = vec_cache.find(name);
+        if (it != vec_cache.end()) return it->second;
+        return vec_cache[name] = upload_vec(c, wt, name, n);
+    }
     std::vector<Sublayer*> mixer_of_layer;   // for kv_from lookups while building
     uint64_t wbytes = 0;
     // pools
@@ -134,15 +172,26 @@ struct Engine final : SeqEngine {
 
     // ---------------------------------------------------------------- weights
     // rows of several [N_i, K] tensors stacked into one matrix in the engine's storage type; absent bias parts are zeros
-    LinearAny load_linear(const WeightTable& wt, const std::vector<std::string>& names, const std::vector<int>& rows, int K, const std::vector<std::string>& biases) {
+    // pad_to > 1: zero rows are appended until N is a multiple of it (so that the tensor-core kernels take the matrix)
+    LinearAny load_linear(const WeightTable& wt, const std::vector<std::string>& names, const std::vector<int>& rows, int K, const std::vector<std::string>& biases, int pad_to = 1) {
+        std::string key = std::to_string(pad_to) + "|";
+        for (auto& nm : names) key += nm + "|";
+        auto hit = lin_cache.find(key);
+        if (hit != lin_cache.end()) return hit->second;
+        LinearAny Lw = load_linear_uncached(wt, names, rows, K, biases, pad_to);
+        lin_cache[key] = Lw;
+        return Lw;
+    }
+    LinearAny load_linear_uncached(const WeightTable& wt, const std::vector<std::string>& names, const std::vector<int>& rows, int K, const std::vector<std::string>& biases, int pad_to) {
         LinearAny Lw;
         Lw.K = K;
         for (int r : rows) Lw.N += r;
+        Lw.N = (Lw.N + pad_to - 1) / pad_to * pad_to;
         const size_t n = (size_t)Lw.N * K;
         bool any_bias = false;
         for (auto& b : biases) any_bias = any_bias || (!b.empty() && wt.has(b));
         if (fp32) {
-            std::vector<float> st(n);
+            std::vector<float> st(n, 0.f);
             size_t o = 0;
             for (size_t i = 0; i < names.size(); ++i) {
                 wt.expect(names[i], {rows[i], K});
@@ -154,7 +203,7 @@ struct Engine final : SeqEngine {
             }
             Lw.w = upload(c, st);
         } else {
-            std::vector<uint16_t> st(n);
+            std::vector<uint16_t> st(n, 0);
             size_t o = 0;
             for (size_t i = 0; i < names.size(); ++i) {
                 wt.expect(names[i], {rows[i], K});
@@ -180,6 +229,38 @@ struct Engine final : SeqEngine {
         }
         return Lw;
     }
+    // A matrix [N, K] in the engine's storage type whose row n is row src[n].second of tensor src[n].first ([., K]): stacks, interleavings.
+    LinearAny load_rows(const WeightTable& wt, const std::string& key, const std::vector<std::pair<const aha_tensor_desc*, int>>& src, int K) {
+        auto hit = lin_cache.find(key);
+        if (hit != lin_cache.end()) return hit->second;
+        LinearAny Lw;
+        Lw.K = K; Lw.N = (int)src.size();
+        const size_t esz = fp32 ? 4 : 2;
+        std::vector<uint8_t> st((size_t)Lw.N * K * esz);
+        for (size_t n = 0; n < src.size(); ++n) {
+            const aha_tensor_desc& d = *src[n].first;
+            const size_t base = (size_t)src[n].second * K;
+            AHA_REQUIRE(base + K <= WeightTable::numel(d), std::string("weight '") + (d.name ? d.name : "?") + "' is smaller than the config says");
+            if (fp32) {
+                float* o = reinterpret_cast<float*>(st.data()) + n * K;
+                for (int k = 0; k < K; ++k) o[k] = WeightTable::at(d, base + k);
+            } else {
+                uint16_t* o = reinterpret_cast<uint16_t*>(st.data()) + n * K;
+                if (d.dtype == AHA_BF16) std::memcpy(o, reinterpret_cast<const uint16_t*>(d.data) + base, (size_t)K * 2);
+                else for (int k = 0; k < K; ++k) { float f = WeightTable::at(d, base + k); uint32_t u; std::memcpy(&u, &f, 4); o[k] = (uint16_t)((u + 0x7FFFu + ((u >> 16) & 1u)) >> 16); }
+            }
+        }
+        Lw.w = upload(c, st);
+        lin_cache[key] = Lw;
+        return Lw;
+    }
+    // batched / grouped products on the CUDA cores (gemm_any.cuh): g carries the batch description, the weights' type is the engine's
+    void gemm_batched(const char* family, int epi, GemmAnyArgs g, double flops, double bytes) {
+        tic(family, flops, bytes);
+        gemm_any(c.stream, epi, fp32, g, c.num_sms);
+        c.cnt.kernels++;
+        toc();
+    }
     // y = epilogue(x W^T + b).  Serving mode with enough rows and a shape that tiles: the library's tcgen05 kernels on bf16 operands -- the
     // fp32 activations are split into bf16 hi + lo halves (16 significant bits), W is the bf16 checkpoint matrix, accumulation is fp32 in
     // TMEM.  Otherwise (exact mode, decode steps, odd sizes): the CUDA-core kernels of gemm_any.cuh.
@@ -203,7 +284,7 @@ struct Engine final : SeqEngine {
             GemmTcArgs t{};
             t.bias = Wt.b; t.resid = nullptr; t.ldr = 0; t.C = C; t.ldc = ldc; t.M = M; t.N = Wt.N; t.K = Wt.K;
             t.act = epi == AEPI_XIELU ? ACT_XIELU : ACT_NONE; t.act_a = a0; t.act_b = a1; t.bf16 = 1; t.group_m = std::max(1, c.gemm_group_m);
-            const int e = epi == AEPI_XIELU ? EPI_ACT : EPI_STORE;
+            const int e = epi == AEPI_XIELU ? EPI_ACT : (epi == AEPI_SWIGLU ? EPI_SWIGLU : EPI_STORE);
             if (c.gemm_pair && Wt.N >= 256 && M >= 1024) gemm_tc3_launch(c.stream, e, hi, lo, Wt.tmap, t, c.num_sms);
             else if (c.gemm_wide && Wt.N >= 256) {
                 if (!Wt.has_tmap256) { Wt.tmap256 = make_tmap_f16_rows(Wt.w, (uint64_t)Wt.N, (uint64_t)Wt.K, 256); Wt.has_tmap256 = true; }
@@ -429,13 +510,28 @@ struct Engine final : SeqEngine {
         cudaStream_t st = c.stream;
         const int T = rb.T;
         if (any_fb) { feedback_tokens_kernel<<<ceil_div(T, 256), 256, 0, st>>>(reinterpret_cast<uint32_t*>(d_meta), d_fb, d_states, T); c.cnt.kernels++; }
-        if (fp32) embed_gather_any_kernel<float><<<T, 128, 0, st>>>(rb.tokens, reinterpret_cast<const float*>(embed), x, W, V);
-        else embed_gather_any_kernel<__nv_bfloat16><<<T, 128, 0, st>>>(rb.tokens, reinterpret_cast<const __nv_bfloat16*>(embed), x, W, V);
+        if (fp32) embed_gather_any_kernel<float><<<T, 128, 0, st>>>(rb.tokens, reinterpret_cast<const float*>(embed), x, W, V, embed_scale);
+        else embed_gather_any_kernel<__nv_bfloat16><<<T, 128, 0, st>>>(rb.tokens, reinterpret_cast<const __nv_bfloat16*>(embed), x, W, V, embed_scale);
         c.cnt.kernels++;
         const int norm_threads = T <= 8 ? std::min(1024, std::max(256, (W / 2 + 31) / 32 * 32)) : 256;      // a decode step has few blocks: more threads for each
         StepView v{this, rb, x, y, h_meta + 4 * Tmax, h_meta + 4 * Tmax + (slots + 1), h_meta + 4 * Tmax + (slots + 1) + slots, cur_span};
         for (int l = 0; l < L; ++l) {
             LayerRec& Ly = layers[l];
+            if (sandwich) {
+                if (Ly.pass >= 0) {
+                    add_row_vector_kernel<<<(unsigned)(((size_t)T * W + 255) / 256), 256, 0, st>>>(x, loop_step + (size_t)Ly.pass * W, W, (size_t)T * W); c.cnt.kernels++;
+                }
+                v.x = sublayer_input(rb, Ly.pre1, Ly.conv1, Ly.tails1);
+                Ly.mixer->run(v);
+                sublayer_output(T, Ly.post1);
+                if (Ly.ff) {
+                    v.x = sublayer_input(rb, Ly.pre2, Ly.conv2, Ly.tails2);
+                    Ly.ff->run(v);
+                    sublayer_output(T, Ly.post2);
+                }
+                if (trace) AHA_CUDA_CHECK(cudaMemcpyAsync(trace_buf + (size_t)l * Tmax * W, x, (size_t)T * W * sizeof(float), cudaMemcpyDeviceToDevice, st));
+                continue;
+            }
             Ly.mixer->run(v);
             tic("norm + residual", 4.0 * T * W, 12.0 * T * W);
             scalar_rmsnorm_add_kernel<<<T, norm_threads, 0, st>>>(x, y, Ly.gain1, eps, W); c.cnt.kernels++;
@@ -452,7 +548,12 @@ struct Engine final : SeqEngine {
         AHA_CUDA_CHECK(cudaGetLastError());
         for (int r0 = 0; r0 < nrows; r0 += Rmax) {
             const int nr = std::min(Rmax, nrows - r0);
-            scalar_rmsnorm_rows_kernel<<<nr, 256, 0, st>>>(x, d_rows + r0, final_gain, eps, hn, W); c.cnt.kernels++;
+            if (sandwich) {
+                GroupNormArgs n{};
+                n.in = x; n.ld_in = W; n.rows = d_rows + r0; n.w = final_w; n.eps = eps; n.C = W; n.groups = norm_groups; n.out = hn; n.ld_out = W; n.mult = logit_scale;
+                group_rmsnorm(st, n, nr);
+            } else scalar_rmsnorm_rows_kernel<<<nr, 256, 0, st>>>(x, d_rows + r0, final_gain, eps, hn, W);
+            c.cnt.kernels++;
             gemm(AEPI_STORE, hn, W, head, logits, V, nr);
             for (int r = 0; r < nr; ++r) {
                 const int gr = r0 + r;
@@ -475,6 +576,48 @@ struct Engine final : SeqEngine {
             if (r0 + nr < nrows) AHA_CUDA_CHECK(cudaStreamSynchronize(st));   // the logits buffer is reused by the next chunk only after its copies have left
         }
         AHA_CUDA_CHECK(cudaGetLastError());
+    }
+
+    // sandwich template: what a sublayer reads, h + conv(h) with h = group norm of the stream.  Decode steps (every entry one token): one launch.
+    const float* sublayer_input(const RaggedBatch& rb, const float* gain, const float* conv_w, float* tails) {
+        cudaStream_t st = c.stream;
+        const int T = rb.T;
+        const size_t tail_stride = (size_t)std::max(0, conv_taps - 1) * W;
+        tic("norm + input convolution", (2.0 * conv_taps + 4.0) * T * W, 4.0 * T * W * (conv_w ? 4.0 : 2.0));
+        const float* res;
+        if (conv_w && rb.E == T && (size_t)W * sizeof(float) <= 160 * 1024) {
+            NormConvArgs a{};
+            a.x = x; a.C = W; a.groups = norm_groups; a.w = gain; a.eps = eps; a.taps = conv_taps; a.cw = conv_w; a.tails = tails; a.tail_slot_stride = tail_stride;
+            a.out = hin; a.rb = rb;
+            static bool attr = false;
+            if (!attr) { AHA_CUDA_CHECK(cudaFuncSetAttribute(norm_conv_single_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024)); attr = true; }
+            norm_conv_single_kernel<<<T, std::min(1024, std::max(128, (W / 2 + 31) / 32 * 32)), (size_t)W * sizeof(float), st>>>(a);
+            c.cnt.kernels++;
+            res = hin;
+        } else {
+            GroupNormArgs n{};
+            n.in = x; n.ld_in = W; n.w = gain; n.eps = eps; n.C = W; n.groups = norm_groups; n.out = hnorm; n.ld_out = W;
+            group_rmsnorm(st, n, T); c.cnt.kernels++;
+            res = hnorm;
+            if (conv_w) {
+                ShortConvArgs a{};
+                a.in = hnorm; a.ld_in = W; a.in_off = 0; a.C = W; a.taps = conv_taps; a.w = conv_w; a.tails = tails; a.tail_slot_stride = tail_stride;
+                a.out = hin; a.ld_out = W; a.out_off = 0; a.add_input = 1; a.rb = rb;
+                c.cnt.kernels += short_conv(st, a, rb.E == T);
+                res = hin;
+            }
+        }
+        AHA_CUDA_CHECK(cudaGetLastError());
+        toc();
+        return res;
+    }
+    // ... and what it leaves: x += m * group norm(y) * gain
+    void sublayer_output(int T, const float* gain) {
+        tic("norm + residual", 4.0 * T * W, 12.0 * T * W);
+        GroupNormArgs n{};
+        n.in = y; n.ld_in = W; n.w = gain; n.eps = eps; n.C = W; n.groups = norm_groups; n.out = x; n.ld_out = W; n.mult = resid_mult; n.add = 1;
+        group_rmsnorm(c.stream, n, T); c.cnt.kernels++;
+        toc();
     }
 
     int prof_n = 0, prof_tps = 0, prof_ctx = 0;   // shape of the profiled step
@@ -716,11 +859,332 @@ struct DenseFF final : Sublayer {
     }
 };
 
+// segments for a recurrence whose longest entry is long (see recurrence.cuh): the longest segments that still give every SM four blocks
+inline void choose_segments(Engine& E, const StepView& v, Hgrn2Args& a, size_t slot_stride) {
+    (void)slot_stride;
+    int longest = 0;
+    for (int e = 0; e < v.rb.E; ++e) longest = std::max(longest, v.h_ent_start[e + 1] - v.h_ent_start[e]);
+    if (longest >= kSegMinEntry && E.seg_state && E.opt.seq_impl == 0 && a.D <= 256) {
+        const int per_seg = a.H * ((a.Dv + kScanCols - 1) / kScanCols);
+        int L = kSegLen;
+        while (L < kSegLenMax && (longest / (2 * L)) * per_seg >= 4 * E.c.num_sms) L *= 2;
+        if (longest > L) { a.seg_state = E.seg_state; a.seg_decay = E.seg_decay; a.seg_len = L; a.seg_max = (longest + L - 1) / L; }
+    }
+}
+
+// Gated linear attention: q = W_q h / sqrt(dim), k = W_k h, v = W_v h, a decay per key channel alpha = sigmoid(z)^(1 / tau) with
+// z = W_a2 (W_a1 h) + b (a low-rank projection); per head S <- diag(alpha) S + k v^T, o = S^T q; o is RMS-normed per head (gain over vdim
+// shared by the heads), multiplied by silu(W_g h) and projected by W_o.  The state is fp32 in the slot pool.
+struct GlaMixer final : Sublayer {
+    Engine& E;
+    int H, D, Dv, r;
+    float tau;
+    LinearAny in, a1, a2, out;
+    float *norm_w = nullptr, *state = nullptr;
+    size_t slot_stride = 0;
+    int ld = 0, z_off = 0;
+    GlaMixer(Engine& e, const Json& mx, const WeightTable& wt, const std::string& p) : E(e) {
+        H = mx.integer("heads"); D = mx.integer("dim"); Dv = mx.integer("vdim"); tau = (float)mx.number("tau");
+        AHA_REQUIRE(H >= 1 && D >= 1 && Dv >= 1 && tau > 0.f, "gla: bad sizes");
+        const aha_tensor_desc& d1 = wt.get(p + "a1");
+        AHA_REQUIRE(d1.rank == 2, "gla: a1 must be a matrix");
+        r = (int)d1.shape[0];
+        in = E.load_linear(wt, {p + "q", p + "k", p + "v", p + "g"}, {H * D, H * D, H * Dv, H * Dv}, E.W, {}, 4);
+        a1 = E.load_linear(wt, {p + "a1"}, {r}, E.W, {});
+        a2 = E.load_linear(wt, {p + "a2"}, {H * D}, r, {p + "a2.b"});
+        out = E.load_linear(wt, {p + "o"}, {E.W}, H * Dv, {});
+        norm_w = E.vec(wt, p + "norm", (size_t)Dv);
+        z_off = in.N;
+        ld = (in.N + H * D + 3) / 4 * 4;
+        slot_stride = (size_t)H * D * Dv;
+        state = E.c.alloc<float>(slot_stride * E.slots);
+        AHA_CUDA_CHECK(cudaMemset(state, 0, slot_stride * E.slots * sizeof(float)));
+        AHA_REQUIRE((D <= 256 && E.opt.seq_impl != 1) || hgrn2_scan_smem(D, Dv) <= 200 * 1024, "gla: dim x vdim state does not fit shared memory");
+        AHA_CUDA_CHECK(cudaFuncSetAttribute(hgrn2_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    }
+    int proj_cols() const override { return ld; }
+    int inner_cols() const override { return std::max(H * Dv, r); }
+    int max_segments() const { return E.Tmax / kSegLen + E.slots; }
+    size_t seg_state_floats() const override { return E.Tmax >= kSegMinEntry ? (size_t)max_segments() * slot_stride : 0; }
+    size_t seg_decay_floats() const override { return E.Tmax >= kSegMinEntry ? (size_t)max_segments() * H * D : 0; }
+    void run(const StepView& v) override {
+        const int T = v.rb.T, HD = H * D;
+        E.gemm(AEPI_STORE, v.x, E.W, in, E.proj, ld, T);
+        E.gemm(AEPI_STORE, v.x, E.W, a1, E.inner, r, T);
+        E.gemm(AEPI_STORE, E.inner, r, a2, E.proj + z_off, ld, T);
+        E.tic("linear recurrence", 4.0 * T * H * D * Dv, 4.0 * T * (3.0 * HD + 3.0 * H * Dv) + 8.0 * v.rb.E * slot_stride);
+        gla_gates_kernel<<<(unsigned)(((size_t)T * HD + 255) / 256), 256, 0, E.c.stream>>>(E.proj, ld, 0, z_off, HD, 1.0f / sqrtf((float)D), 1.0f / tau, (size_t)T * HD);
+        E.c.cnt.kernels++;
+        Hgrn2Args a{};
+        a.qfv = E.proj; a.ld = ld; a.q_off = 0; a.k_off = HD; a.f_off = z_off; a.v = E.proj; a.ld_v = ld; a.v_off = 2 * HD; a.gates_done = 1;
+        a.norm_w = norm_w; a.eps = E.eps; a.out_gate = E.proj + 2 * HD + H * Dv; a.out_gate_ld = ld;
+        a.state = state; a.slot_stride = slot_stride; a.out = E.inner; a.H = H; a.D = D; a.Dv = Dv; a.rb = v.rb;
+        choose_segments(E, v, a, slot_stride);
+        E.c.cnt.kernels += hgrn2_scan(E.c.stream, a, E.opt.seq_impl);
+        E.toc();
+        E.gemm(AEPI_STORE, E.inner, H * Dv, out, v.y, E.W, T);
+    }
+};
+
+// Mamba-2: W_in h = [z | x | B | C | dt]; x, B, C pass a short causal convolution (bias, silu); dt = softplus(dt + dt_bias); per head (with the
+// B and C of its group) S <- exp(-exp(A_log) dt) S + dt B x^T, y = S^T C + D x; y * silu(z) is RMS-normed in groups, then W_o.  The recurrence
+// is the keyed diagonal scan with the scalar decay repeated over the state channels.  State and convolution tail are fp32 in the slot pool.
+struct Mamba2Mixer final : Sublayer {
+    Engine& E;
+    int H, P, N, G, NG, taps, inner, Cc, n_in;
+    LinearAny in, out;
+    float *conv_w = nullptr, *conv_b = nullptr, *dt_bias = nullptr, *a_log = nullptr, *Dw = nullptr, *norm_w = nullptr, *state = nullptr, *tails = nullptr;
+    size_t slot_stride = 0, tail_stride = 0;
+    int ld = 0, s_off = 0;
+    Mamba2Mixer(Engine& e, const Json& mx, const WeightTable& wt, const std::string& p) : E(e) {
+        H = mx.integer("heads"); P = mx.integer("vdim"); N = mx.integer("state"); G = mx.integer_or("groups", 1); NG = mx.integer_or("norm_groups", 1);
+        AHA_REQUIRE(H >= 1 && P >= 1 && N >= 1 && G >= 1 && H % G == 0 && NG >= 1 && (H * P) % NG == 0, "mamba2: bad sizes");
+        inner = H * P; Cc = inner + 2 * G * N; n_in = 2 * inner + 2 * G * N + H;
+        const aha_tensor_desc& dc = wt.get(p + "conv");
+        AHA_REQUIRE(dc.rank == 2 && dc.shape[0] == Cc, "mamba2: conv must be [channels, taps]");
+        taps = (int)dc.shape[1];
+        AHA_REQUIRE(taps >= 1 && taps <= kShortConvMaxTaps, "mamba2: between 1 and 16 convolution taps");
+        in = E.load_linear(wt, {p + "in"}, {n_in}, E.W, {}, 32);
+        out = E.load_linear(wt, {p + "o"}, {E.W}, inner, {});
+        conv_w = E.vec(wt, p + "conv", (size_t)Cc * taps);
+        conv_b = wt.has(p + "conv.b") ? E.vec(wt, p + "conv.b", (size_t)Cc) : nullptr;
+        dt_bias = E.vec(wt, p + "dt_bias", (size_t)H); a_log = E.vec(wt, p + "A_log", (size_t)H); Dw = E.vec(wt, p + "D", (size_t)H);
+        norm_w = E.vec(wt, p + "norm", (size_t)inner);
+        s_off = in.N; ld = in.N + 3 * H * N;
+        slot_stride = (size_t)H * N * P;
+        state = E.c.alloc<float>(slot_stride * E.slots);
+        AHA_CUDA_CHECK(cudaMemset(state, 0, slot_stride * E.slots * sizeof(float)));
+        tail_stride = (size_t)(taps - 1) * Cc;
+        tails = E.c.alloc<float>(std::max<size_t>(1, tail_stride * E.slots));
+        AHA_CUDA_CHECK(cudaMemset(tails, 0, std::max<size_t>(1, tail_stride * E.slots) * sizeof(float)));
+        AHA_REQUIRE((N <= 256 && E.opt.seq_impl != 1) || hgrn2_scan_smem(N, P) <= 200 * 1024, "mamba2: state x vdim does not fit shared memory");
+        AHA_CUDA_CHECK(cudaFuncSetAttribute(hgrn2_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    }
+    int proj_cols() const override { return ld; }
+    int inner_cols() const override { return inner; }
+    int q_cols() const override { return Cc; }
+    int max_segments() const { return E.Tmax / kSegLen + E.slots; }
+    size_t seg_state_floats() const override { return E.Tmax >= kSegMinEntry ? (size_t)max_segments() * slot_stride : 0; }
+    size_t seg_decay_floats() const override { return E.Tmax >= kSegMinEntry ? (size_t)max_segments() * H * N : 0; }
+    void run(const StepView& v) override {
+        const int T = v.rb.T, HN = H * N;
+        cudaStream_t st = E.c.stream;
+        E.gemm(AEPI_STORE, v.x, E.W, in, E.proj, ld, T);
+        E.tic("short convolution", 2.0 * T * Cc * taps, 8.0 * T * Cc);
+        ShortConvArgs cv{};
+        cv.in = E.proj; cv.ld_in = ld; cv.in_off = inner; cv.C = Cc; cv.taps = taps; cv.w = conv_w; cv.bias = conv_b; cv.tails = tails; cv.tail_slot_stride = tail_stride;
+        cv.out = E.qbuf; cv.ld_out = Cc; cv.out_off = 0; cv.silu = 1; cv.rb = v.rb;
+        E.c.cnt.kernels += short_conv(st, cv, v.rb.E == T);
+        E.toc();
+        E.tic("linear recurrence", 4.0 * T * H * N * P, 4.0 * T * (6.0 * HN + 2.0 * inner) + 8.0 * v.rb.E * slot_stride);
+        Mamba2GateArgs g{};
+        g.dt_raw = E.proj + 2 * inner + 2 * G * N; g.ld_dt = ld; g.bc = E.qbuf; g.ld_bc = Cc; g.b_off = inner; g.c_off = inner + G * N;
+        g.dt_bias = dt_bias; g.a_log = a_log; g.out = E.proj; g.ld_out = ld; g.q_off = s_off; g.f_off = s_off + HN; g.k_off = s_off + 2 * HN;
+        g.H = H; g.G = G; g.N = N; g.T = T;
+        mamba2_gates_kernel<<<(unsigned)(((size_t)T * HN + 255) / 256), 256, 0, st>>>(g);
+        E.c.cnt.kernels++;
+        Hgrn2Args a{};
+        a.qfv = E.proj; a.ld = ld; a.q_off = g.q_off; a.f_off = g.f_off; a.k_off = g.k_off; a.v = E.qbuf; a.ld_v = Cc; a.v_off = 0; a.gates_done = 1;
+        a.norm_w = nullptr; a.eps = E.eps; a.state = state; a.slot_stride = slot_stride; a.out = E.inner; a.H = H; a.D = N; a.Dv = P; a.rb = v.rb;
+        choose_segments(E, v, a, slot_stride);
+        E.c.cnt.kernels += hgrn2_scan(st, a, E.opt.seq_impl);
+        // (y + D x) * silu(z), RMS norm in groups, gain: in place
+        GroupNormArgs n{};
+        n.in = E.inner; n.ld_in = inner; n.gate = E.proj; n.ld_gate = ld; n.skip = E.qbuf; n.ld_skip = Cc; n.skip_w = Dw; n.skip_span = P;
+        n.w = norm_w; n.eps = E.eps; n.C = inner; n.groups = NG; n.out = E.inner; n.ld_out = inner;
+        group_rmsnorm(st, n, T); E.c.cnt.kernels++;
+        E.toc();
+        E.gemm(AEPI_STORE, E.inner, inner, out, v.y, E.W, T);
+    }
+};
+
+// Latent attention (see attention_latent.cuh): the cache holds [latent | rotated key part] per token; a head's query is absorbed through
+// W_uk, its output expanded through W_uv; sigmoid output gate from the mixer's input; causal, ordinary softmax.
+struct LatentAttentionMixer final : Sublayer {
+    Engine& E;
+    int H, D, R, Dv, rank;
+    float scale, rot_mult = 1.f;
+    LinearAny in, out, uk_t, uv;
+    int q_off = 0, dkv_off = 0, g_off = 0, n_freq = 0;
+    float *c_norm = nullptr, *freq = nullptr;
+    PagedKV kv;
+    LatentAttentionMixer(Engine& e, const Json& mx, const WeightTable& wt, const std::string& p) : E(e) {
+        H = mx.integer("heads"); D = mx.integer("dim"); R = mx.integer("rot_dim"); Dv = mx.integer("vdim"); rank = mx.integer("kv_rank");
+        AHA_REQUIRE(H >= 1 && D >= 1 && R >= 0 && Dv >= 1 && rank >= 1, "latent attention: bad sizes");
+        scale = (float)mx.number("scale");
+        q_off = 0; dkv_off = H * (D + R); g_off = dkv_off + rank + R;
+        in = E.load_linear(wt, {p + "q", p + "dkv", p + "g"}, {H * (D + R), rank + R, H * Dv}, E.W, {}, 32);
+        out = E.load_linear(wt, {p + "o"}, {E.W}, H * Dv, {});
+        c_norm = E.vec(wt, p + "dkv.norm", (size_t)rank);
+        // W_uk [H * D, rank] transposed head by head: row h * rank + r holds column r of the head's rows
+        {
+            wt.expect(p + "uk", {H * D, rank});
+            wt.expect(p + "uv", {H * Dv, rank});
+            const std::string key = p + "uk^T";
+            auto hit = E.lin_cache.find(key);
+            if (hit != E.lin_cache.end()) uk_t = hit->second;
+            else {
+                const aha_tensor_desc& d = wt.get(p + "uk");
+                std::vector<float> tr((size_t)H * rank * D);
+                for (int h = 0; h < H; ++h)
+                    for (int r = 0; r < rank; ++r)
+                        for (int k = 0; k < D; ++k) tr[((size_t)h * rank + r) * D + k] = WeightTable::at(d, ((size_t)h * D + k) * rank + r);
+                aha_tensor_desc td{};
+                td.name = "uk^T"; td.data = tr.data(); td.dtype = AHA_F32; td.rank = 2; td.shape[0] = (int64_t)H * rank; td.shape[1] = D;
+                std::vector<std::pair<const aha_tensor_desc*, int>> src;
+                for (int n = 0; n < H * rank; ++n) src.push_back({&td, n});
+                uk_t = E.load_rows(wt, key, src, D);
+            }
+            uv = E.load_linear(wt, {p + "uv"}, {H * Dv}, rank, {});
+        }
+        std::vector<float> fr;
+        if (R > 0) {
+            const Json& rot = mx.at("rot");
+            const int dims = rot.integer_or("dims", R);
+            AHA_REQUIRE(dims >= 0 && dims <= R && dims % 2 == 0, "latent attention: rot.dims must be even and at most rot_dim");
+            if (dims > 0) {
+                if (rot.has("scaling")) {
+                    const Json& sc = rot.at("scaling");
+                    yarn_frequencies(dims, rot.number("base"), sc.number("factor"), sc.number("original"), sc.number("fast"), sc.number("slow"), fr, rot_mult);
+                } else yarn_frequencies(dims, rot.number("base"), 0.0, 0.0, 0.0, 0.0, fr, rot_mult);
+            }
+        }
+        n_freq = (int)fr.size();
+        if (fr.empty()) fr.push_back(0.f);
+        freq = upload(E.c, fr);
+        kv.G = 1; kv.D = rank + R; kv.Dv = rank; kv.ldv = rank + R;
+        const size_t nk = (size_t)E.num_pages * kPage * kv.D;
+        kv.k = E.c.alloc<float>(nk);
+        kv.v = kv.k;
+        AHA_CUDA_CHECK(cudaMemset(kv.k, 0, nk * sizeof(float)));
+    }
+    int proj_cols() const override { return in.N; }
+    int inner_cols() const override { return H * rank; }
+    int q_cols() const override { return std::max(H * (rank + R), H * Dv); }
+    size_t attn_part_floats() const override { return window_attn_part_floats(H, rank); }
+    uint64_t kv_bytes_per_token() const override { return 4ull * (rank + R); }
+    void run(const StepView& v) override {
+        const int T = v.rb.T, ld = in.N, ldq = H * (rank + R);
+        cudaStream_t st = E.c.stream;
+        E.gemm(AEPI_STORE, v.x, E.W, in, E.proj, ld, T);
+        E.tic("latent norm + rotary + cache write", 8.0 * T * (rank + (H + 1) * R), 8.0 * T * (rank + (H + 1) * R));
+        LatentPrepArgs a{};
+        a.proj = E.proj; a.ld = ld; a.q_off = q_off; a.dkv_off = dkv_off; a.H = H; a.D = D; a.R = R; a.rank = rank; a.c_norm = c_norm; a.eps = E.eps;
+        a.freq = freq; a.n_freq = n_freq; a.mult = rot_mult; a.q_abs = E.qbuf; a.ld_q = ldq; a.kv = kv; a.rb = v.rb;
+        latent_prep_kernel<<<T, T <= 8 ? 512 : 128, 0, st>>>(a);
+        E.c.cnt.kernels++;
+        AHA_CUDA_CHECK(cudaGetLastError());
+        E.toc();
+        {   // q_abs[t][h][:rank] = W_uk(h)^T q_plain[t][h]
+            GemmAnyArgs g{};
+            g.A = E.proj + q_off; g.lda = ld; g.W = uk_t.w; g.C = E.qbuf; g.ldc = ldq; g.M = T; g.N = rank; g.K = D;
+            g.batch = H; g.a_bs = (size_t)(D + R); g.w_bs = (size_t)rank * D; g.c_bs = (size_t)(rank + R);
+            E.gemm_batched("per-head latent products", AEPI_STORE, g, 2.0 * T * H * rank * D, (double)H * rank * D * (E.fp32 ? 4 : 2) + 4.0 * T * H * (D + rank));
+        }
+        WindowAttnArgs w{};
+        w.q = E.qbuf; w.kv = kv; w.slopes = nullptr; w.scale = scale; w.window = 0; w.gate = nullptr; w.out = E.inner; w.H = H; w.rb = v.rb;
+        w.part = E.opt.seq_impl == 1 ? nullptr : E.attn_part;
+        E.tic("latent attention", 2.0 * E.prof_pairs(0) * H * (2.0 * rank + R), 4.0 * (T * (double)H * (2.0 * rank + R) + E.prof_unique(0) * (rank + R)));
+        E.c.cnt.kernels += window_attn(st, w, v.span);
+        E.toc();
+        {   // o[t][h] = W_uv(h) o_latent[t][h]
+            GemmAnyArgs g{};
+            g.A = E.inner; g.lda = H * rank; g.W = uv.w; g.C = E.qbuf; g.ldc = H * Dv; g.M = T; g.N = Dv; g.K = rank;
+            g.batch = H; g.a_bs = (size_t)rank; g.w_bs = (size_t)Dv * rank; g.c_bs = (size_t)Dv;
+            E.gemm_batched("per-head latent products", AEPI_STORE, g, 2.0 * T * H * rank * Dv, (double)H * rank * Dv * (E.fp32 ? 4 : 2) + 4.0 * T * H * (Dv + rank));
+        }
+        E.tic("output gate", 4.0 * T * H * Dv, 12.0 * T * H * Dv);
+        gate_mul_kernel<<<(unsigned)(((size_t)T * H * Dv + 255) / 256), 256, 0, st>>>(E.qbuf, H * Dv, E.proj + g_off, ld, H * Dv, (size_t)T * H * Dv, 0);
+        E.c.cnt.kernels++;
+        E.toc();
+        E.gemm(AEPI_STORE, E.qbuf, H * Dv, out, v.y, E.W, T);
+    }
+};
+
+// Mixture of experts chosen by a table: row `token id` of '.table' names the token's `top` experts, each weighted 1 / top.  Expert:
+// W_down (silu(W_gate h) * (W_up h)).  The experts' gate and up rows are interleaved into one matrix per expert (the gate / up epilogue),
+// all experts stacked, so that the products are batched (decode steps: one row per assignment with its expert's matrix) or grouped
+// (assignments ordered by expert on the device, a batch per expert over its rows).
+struct TableMoeFF final : Sublayer {
+    Engine& E;
+    int ff, experts, top, table_ld;
+    LinearAny gu, down;     // [experts * 2 ff, W], [experts * W, ff]
+    int* table = nullptr;
+    int* tok_of_assign = nullptr;   // [kGraphMaxTokens * top]: assignment a belongs to packed token a / top
+    int* err = nullptr;
+    TableMoeFF(Engine& e, const Json& cfg, const WeightTable& wt, const std::string& p) : E(e) {
+        ff = cfg.at("expert").integer("ff"); experts = cfg.at("router").integer("experts"); top = cfg.at("router").integer("top");
+        AHA_REQUIRE(ff >= 1 && experts >= 1 && top >= 1 && top <= experts, "moe: bad sizes");
+        std::vector<std::pair<const aha_tensor_desc*, int>> s1, s2;
+        for (int x = 0; x < experts; ++x) {
+            const std::string q = p + "e" + std::to_string(x) + ".";
+            wt.expect(q + "gate", {ff, E.W}); wt.expect(q + "up", {ff, E.W}); wt.expect(q + "down", {E.W, ff});
+            for (int j = 0; j < ff; ++j) { s1.push_back({&wt.get(q + "gate"), j}); s1.push_back({&wt.get(q + "up"), j}); }
+            for (int j = 0; j < E.W; ++j) s2.push_back({&wt.get(q + "down"), j});
+        }
+        gu = E.load_rows(wt, p + "gate/up", s1, E.W);
+        down = E.load_rows(wt, p + "down", s2, ff);
+        const aha_tensor_desc& dt = wt.get(p + "table");
+        AHA_REQUIRE(dt.rank == 2 && dt.shape[0] == E.V && dt.shape[1] >= top, "moe: table must be [vocab, top]");
+        table_ld = (int)dt.shape[1];
+        const std::string tkey = p + "table";
+        auto hit = E.int_cache.find(tkey);
+        if (hit != E.int_cache.end()) table = hit->second;
+        else {
+            std::vector<int> tb((size_t)E.V * table_ld);
+            for (size_t i = 0; i < tb.size(); ++i) {
+                tb[i] = (int)std::llround(WeightTable::at(dt, i));
+                AHA_REQUIRE(tb[i] >= 0 && tb[i] < experts, "moe: a table entry names no expert");
+            }
+            table = E.int_cache[tkey] = upload(E.c, tb);
+        }
+        std::vector<int> ta((size_t)kGraphMaxTokens * top);
+        for (size_t i = 0; i < ta.size(); ++i) ta[i] = (int)(i / top);
+        tok_of_assign = upload(E.c, ta);
+        err = E.c.alloc<int>(1);
+        AHA_CUDA_CHECK(cudaMemset(err, 0, sizeof(int)));
+    }
+    int proj_cols() const override { return top * ff; }
+    int inner_cols() const override { return top * E.W; }
+    size_t route_ints() const override { return 3 * (size_t)E.Tmax * top + experts + 1; }
+    void run(const StepView& v) override {
+        const int T = v.rb.T, A = T * top, W = E.W;
+        cudaStream_t st = E.c.stream;
+        int* expert_of = E.route_buf; int* sorted_tok = expert_of + (size_t)E.Tmax * top; int* place_of = sorted_tok + (size_t)E.Tmax * top; int* offsets = place_of + (size_t)E.Tmax * top;
+        const bool rows = T <= kGraphMaxTokens && E.opt.seq_impl != 1;      // decode-sized steps: a batch per assignment, no ordering
+        E.tic("expert routing (table)", 0.0, 16.0 * A);
+        MoeRouteArgs r{};
+        r.tokens = v.rb.tokens; r.T = T; r.table = table; r.table_ld = table_ld; r.V = E.V; r.top = top; r.experts = experts;
+        r.expert_of = expert_of; r.offsets = offsets; r.sorted_tok = sorted_tok; r.place_of = place_of; r.error = err; r.sort = rows ? 0 : 1;
+        moe_table_route(st, r); E.c.cnt.kernels++;
+        E.toc();
+        const double wb = E.fp32 ? 4.0 : 2.0, used = std::min(A, experts);
+        GemmAnyArgs g{};
+        g.A = v.x; g.lda = W; g.W = gu.w; g.C = E.proj; g.ldc = ff; g.N = 2 * ff; g.K = W; g.w_bs = (size_t)2 * ff * W;
+        if (rows) { g.M = 1; g.batch = A; g.a_index = tok_of_assign; g.a_bs = (size_t)W; g.w_index = expert_of; g.c_bs = (size_t)ff; }
+        else { g.M = A; g.batch = experts; g.row_offsets = offsets; g.a_gather = sorted_tok; }
+        E.gemm_batched(rows ? "expert linear (decode rows)" : "expert linear (grouped, CUDA cores)", AEPI_SWIGLU, g, 4.0 * A * ff * W, used * 2.0 * ff * W * wb + 4.0 * A * (W + ff));
+        GemmAnyArgs d{};
+        d.A = E.proj; d.lda = ff; d.W = down.w; d.C = E.inner; d.ldc = W; d.N = W; d.K = ff; d.w_bs = (size_t)W * ff;
+        if (rows) { d.M = 1; d.batch = A; d.a_bs = (size_t)ff; d.w_index = expert_of; d.c_bs = (size_t)W; }
+        else { d.M = A; d.batch = experts; d.row_offsets = offsets; }
+        E.gemm_batched(rows ? "expert linear (decode rows)" : "expert linear (grouped, CUDA cores)", AEPI_STORE, d, 2.0 * A * ff * W, used * ff * W * wb + 4.0 * A * (W + ff));
+        E.tic("expert combine", 1.0 * A * W, 4.0 * (A + T) * W);
+        moe_combine_kernel<<<(unsigned)(((size_t)T * W + 255) / 256), 256, 0, st>>>(E.inner, rows ? nullptr : place_of, v.y, W, top, 1.0f / (float)top, (size_t)T * W);
+        E.c.cnt.kernels++;
+        AHA_CUDA_CHECK(cudaGetLastError());
+        E.toc();
+    }
+};
+
 using MixerFactory = std::function<std::unique_ptr<Sublayer>(Engine&, const Json&, const WeightTable&, const std::string&, int)>;
 const std::map<std::string, MixerFactory>& mixer_registry() {
     static const std::map<std::string, MixerFactory> r = {
         {"hgrn2", [](Engine& e, const Json& mx, const WeightTable& wt, const std::string& p, int) { return std::unique_ptr<Sublayer>(new Hgrn2Mixer(e, mx, wt, p)); }},
         {"attention", [](Engine& e, const Json& mx, const WeightTable& wt, const std::string& p, int l) { return std::unique_ptr<Sublayer>(new WindowAttentionMixer(e, mx, wt, p, l)); }},
+        {"gla", [](Engine& e, const Json& mx, const WeightTable& wt, const std::string& p, int) { return std::unique_ptr<Sublayer>(new GlaMixer(e, mx, wt, p)); }},
+        {"mamba2", [](Engine& e, const Json& mx, const WeightTable& wt, const std::string& p, int) { return std::unique_ptr<Sublayer>(new Mamba2Mixer(e, mx, wt, p)); }},
+        {"latent_attention", [](Engine& e, const Json& mx, const WeightTable& wt, const std::string& p, int) { return std::unique_ptr<Sublayer>(new LatentAttentionMixer(e, mx, wt, p)); }},
     };
     return r;
 }
@@ -728,6 +1192,7 @@ using FFFactory = std::function<std::unique_ptr<Sublayer>(Engine&, const Json&, 
 const std::map<std::string, FFFactory>& ff_registry() {
     static const std::map<std::string, FFFactory> r = {
         {"dense", [](Engine& e, const Json& cfg, const WeightTable& wt, const std::string& p) { return std::unique_ptr<Sublayer>(new DenseFF(e, cfg, wt, p)); }},
+        {"moe", [](Engine& e, const Json& cfg, const WeightTable& wt, const std::string& p) { return std::unique_ptr<Sublayer>(new TableMoeFF(e, cfg, wt, p)); }},
     };
     return r;
 }
@@ -745,7 +1210,38 @@ SeqEngine* make_layered_engine(Ctx& ctx, const Json& cfg, const WeightTable& wt,
     e.eps = (float)cfg.at("norm").number("eps");
     const Json& ls = cfg.at("layers");
     AHA_REQUIRE(ls.kind == Json::Arr && !ls.arr.empty(), "config.json: 'layers' must be a non-empty list");
-    e.L = (int)ls.arr.size();
+    // the layer template
+    std::string arch = cfg.string_or("architecture", "");
+    for (auto& ch : arch) ch = (char)std::tolower((unsigned char)ch);
+    e.sandwich = arch == "gatuzen";
+    // the runs: layers before the loop once, the loop's span `times` times, the rest once
+    std::vector<std::pair<int, int>> runs;      // (layer, pass it opens or -1)
+    {
+        const int nl = (int)ls.arr.size();
+        int start = 0, stop = 0, times = 1;
+        if (cfg.has("loop")) {
+            const Json& lp = cfg.at("loop");
+            start = lp.integer("start"); stop = lp.integer("stop"); times = lp.integer("times");
+            AHA_REQUIRE(e.sandwich, "config.json: 'loop' is only known to the sandwich layer template");
+            AHA_REQUIRE(0 <= start && start <= stop && stop <= nl && times >= 1, "config.json: bad 'loop'");
+        }
+        for (int l = 0; l < start; ++l) runs.push_back({l, -1});
+        if (stop > start)
+            for (int t = 0; t < times; ++t)
+                for (int l = start; l < stop; ++l) runs.push_back({l, l == start ? t : -1});
+        for (int l = stop; l < nl; ++l) runs.push_back({l, -1});
+        if (stop > start) e.loop_step = e.vec(wt, "loop.step", (size_t)times * e.W);
+    }
+    e.L = (int)runs.size();
+    if (e.sandwich) {
+        e.norm_groups = cfg.at("norm").integer_or("groups", 1);
+        AHA_REQUIRE(e.norm_groups >= 1 && e.W % e.norm_groups == 0, "config.json: norm.groups must divide the width");
+        e.resid_mult = (float)cfg.number_or("residual_mult", 1.0);
+        e.logit_scale = (float)cfg.number_or("logit_scale", 1.0);
+        if (cfg.has("embedding")) e.embed_scale = (float)cfg.at("embedding").number_or("scale", 1.0);
+        e.conv_taps = cfg.has("canon") ? cfg.at("canon").integer("taps") : 0;
+        AHA_REQUIRE(e.conv_taps >= 0 && e.conv_taps <= kShortConvMaxTaps, "config.json: canon.taps must be at most 16");
+    }
     e.slots = std::max(1, opt.max_seqs);
     e.num_pages = std::max(1, ceil_div(std::max(1, opt.max_tokens), kPage));
     e.max_pages = e.num_pages;
@@ -753,9 +1249,12 @@ SeqEngine* make_layered_engine(Ctx& ctx, const Json& cfg, const WeightTable& wt,
     e.Rmax = std::min(e.Tmax, 128);
     e.embed = e.load_linear(wt, {"embed"}, {e.V}, e.W, {}).w;
     e.head = e.load_linear(wt, {"head"}, {e.V}, e.W, {});
-    e.final_gain = upload_scalar(e, wt, "final.norm");
+    if (e.sandwich) e.final_w = e.vec(wt, "final.norm", (size_t)e.W);
+    else e.final_gain = upload_scalar(e, wt, "final.norm");
     int proj_cols = 1, inner_cols = 1, q_cols = 1;
-    for (int l = 0; l < e.L; ++l) {
+    size_t route_ints = 0;
+    for (int r = 0; r < e.L; ++r) {
+        const int l = runs[r].first;
         const Json& ly = ls.arr[l];
         const std::string p = "l" + std::to_string(l) + ".";
         const std::string type = ly.string_or("type", "");
@@ -764,14 +1263,29 @@ SeqEngine* make_layered_engine(Ctx& ctx, const Json& cfg, const WeightTable& wt,
         Engine::LayerRec rec;
         rec.mixer = it->second(e, ly.at("mixer"), wt, p + "mix.", l);
         e.mixer_of_layer.push_back(rec.mixer.get());
-        rec.gain1 = upload_scalar(e, wt, p + "norm1");
+        rec.pass = runs[r].second;
+        auto conv_state = [&](const std::string& name, float*& w, float*& tails) {
+            if (e.conv_taps < 1 || !wt.has(name)) return;
+            w = e.vec(wt, name, (size_t)e.W * e.conv_taps);
+            const size_t n = std::max<size_t>(1, (size_t)(e.conv_taps - 1) * e.W * e.slots);
+            tails = ctx.alloc<float>(n);
+            AHA_CUDA_CHECK(cudaMemset(tails, 0, n * sizeof(float)));
+        };
+        if (e.sandwich) {
+            rec.pre1 = e.vec(wt, p + "norm1", (size_t)e.W); rec.post1 = e.vec(wt, p + "norm1b", (size_t)e.W);
+            conv_state(p + "canon1", rec.conv1, rec.tails1);
+        } else rec.gain1 = upload_scalar(e, wt, p + "norm1");
         if (ly.has("mlp")) {
             const Json& ml = ly.at("mlp");
             const std::string kind = ml.string_or("kind", "");
             auto jt = ff_registry().find(kind);
             AHA_REQUIRE(jt != ff_registry().end(), "config.json: layer " + std::to_string(l) + " has an unknown feed-forward kind '" + kind + "'");
             rec.ff = jt->second(e, ml, wt, p + "mlp.");
-            rec.gain2 = upload_scalar(e, wt, p + "norm2");
+            if (e.sandwich) {
+                rec.pre2 = e.vec(wt, p + "norm2", (size_t)e.W); rec.post2 = e.vec(wt, p + "norm2b", (size_t)e.W);
+                conv_state(p + "canon2", rec.conv2, rec.tails2);
+            } else rec.gain2 = upload_scalar(e, wt, p + "norm2");
+            route_ints = std::max(route_ints, rec.ff->route_ints());
         }
         for (Sublayer* s : {rec.mixer.get(), rec.ff.get()})
             if (s) { proj_cols = std::max(proj_cols, s->proj_cols()); inner_cols = std::max(inner_cols, s->inner_cols()); q_cols = std::max(q_cols, s->q_cols()); }
@@ -786,6 +1300,8 @@ SeqEngine* make_layered_engine(Ctx& ctx, const Json& cfg, const WeightTable& wt,
     AHA_CUDA_CHECK(cudaMemset(e.d_tables, 0, (size_t)e.slots * e.max_pages * sizeof(int)));
     const size_t T = e.Tmax;
     e.x = ctx.alloc<float>(T * e.W); e.y = ctx.alloc<float>(T * e.W);
+    if (e.sandwich) { e.hnorm = ctx.alloc<float>(T * e.W); e.hin = ctx.alloc<float>(T * e.W); }
+    if (route_ints) e.route_buf = ctx.alloc<int>(route_ints);
     e.proj = ctx.alloc<float>(T * proj_cols); e.inner = ctx.alloc<float>(T * inner_cols); e.qbuf = ctx.alloc<float>(T * q_cols);
     if (!e.fp32) { gemm_tc_init(); flash_attn_tc_init(); ctx.split_buf(T * (size_t)std::max({e.W, proj_cols, inner_cols})); }
     size_t part = 0;

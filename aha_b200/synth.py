@@ -330,7 +330,7 @@ def make_malasun(cfg, seed=0, fast=False):
 
 
 def make_weights(kind, cfg, seed=0):
-    return {"qwen3": make_qwen3, "qwen3vl": make_qwen3vl, "qwen3_asr": make_qwen3_asr, "malasun": make_malasun}[kind](cfg, seed)
+    return {"qwen3": make_qwen3, "qwen3vl": make_qwen3vl, "qwen3_asr": make_qwen3_asr, "malasun": make_malasun, "gatuzen": make_gatuzen}[kind](cfg, seed)
 
 
 # ----------------------------------------------------------------------------- synthetic inputs
@@ -413,3 +413,120 @@ def asr_prompt_ids(cfg, n_audio_tokens, n_text=8, seed=4):
     post = synth_text_ids(n_text - n_text // 2, min(V, 151000), seed + 1, avoid=special).tolist()
     ids = pre + [tk["audio_start_token_id"]] + [tk["audio_token_id"]] * n_audio_tokens + [tk["audio_end_token_id"]] + post
     return np.asarray(ids, dtype=np.uint32)
+
+
+# ----------------------------------------------------------------------------- Gatuzen (layered engine, sandwich template)
+def gatuzen_config(layers, width=64, vocab=96, eps=1e-5, groups=2, taps=3, residual_mult=0.5, embed_scale=1.0, logit_scale=1.0, loop=None):
+    """config.json of a Gatuzen model.  layers: list of dicts with "type" and the mixer's sizes,
+         {"type": "gla", "heads", "dim", "vdim", "tau", "rank"}          (rank: rows of the low-rank decay projection, a tensor shape only)
+         {"type": "mamba2", "heads", "vdim", "state", "groups", "norm_groups", "conv"}
+         {"type": "latent_attention", "heads", "dim", "rot_dim", "vdim", "kv_rank", "scale", "base", "scaling": None | dict}
+       each with "moe": None | {"experts", "top", "ff"}.  loop: None | (start, stop, times)."""
+    out = []
+    for ly in layers:
+        t = ly["type"]
+        if t == "gla":
+            mx = {"heads": ly["heads"], "dim": ly["dim"], "vdim": ly["vdim"], "tau": float(ly.get("tau", 16.0))}
+        elif t == "mamba2":
+            mx = {"heads": ly["heads"], "vdim": ly["vdim"], "state": ly["state"], "groups": ly.get("groups", 1), "norm_groups": ly.get("norm_groups", 1),
+                  "conv": ly.get("conv", 4)}
+        elif t == "latent_attention":
+            rot = {"base": float(ly.get("base", 10000.0)), "dims": ly["rot_dim"]}
+            if ly.get("scaling"):
+                rot["scaling"] = dict(ly["scaling"])
+            mx = {"heads": ly["heads"], "dim": ly["dim"], "rot_dim": ly["rot_dim"], "vdim": ly["vdim"], "kv_rank": ly["kv_rank"], "rot": rot,
+                  "scale": float(ly.get("scale", (ly["dim"] + ly["rot_dim"]) ** -0.5))}
+        else:
+            raise ValueError(t)
+        moe = ly.get("moe")
+        out.append({"type": t, "mixer": mx, "_rank": ly.get("rank", 8),
+                    "mlp": {"kind": "moe", "expert": {"ff": moe["ff"]}, "router": {"experts": moe["experts"], "top": moe["top"]}} if moe else None})
+    cfg = {"architecture": "Gatuzen", "layers": out, "norm": {"eps": eps, "groups": groups}, "canon": {"taps": taps}, "residual_mult": residual_mult,
+           "embedding": {"scale": embed_scale}, "logit_scale": logit_scale, "vocab": vocab, "width": width}
+    if loop:
+        cfg["loop"] = {"start": loop[0], "stop": loop[1], "times": loop[2]}
+    return cfg
+
+
+def gatuzen_shape(width, n_layers, heads, head_dim, ff, experts, top, vocab=32000, state=64, kv_rank=256, rot_dim=32, taps=4, loop=None):
+    """A layer list of the sizes a served model would have: gla, mamba2 and latent-attention layers in turn, every layer with experts."""
+    layers = []
+    moe = {"experts": experts, "top": top, "ff": ff}
+    for i in range(n_layers):
+        k = i % 3
+        if k == 0:
+            layers.append({"type": "gla", "heads": heads, "dim": head_dim, "vdim": head_dim, "tau": 8.0, "rank": 32, "moe": moe})
+        elif k == 1:
+            layers.append({"type": "mamba2", "heads": heads, "vdim": head_dim, "state": state, "groups": max(1, heads // 8), "norm_groups": 2, "conv": 4, "moe": moe})
+        else:
+            layers.append({"type": "latent_attention", "heads": heads, "dim": head_dim, "rot_dim": rot_dim, "vdim": head_dim, "kv_rank": kv_rank, "base": 5e5,
+                           "scaling": {"factor": 8.0, "original": 4096, "fast": 16.0, "slow": 2.0}, "moe": moe})
+    return gatuzen_config(layers, width=width, vocab=vocab, eps=1e-6, groups=2, taps=taps, residual_mult=0.5, embed_scale=0.75, logit_scale=1.5, loop=loop)
+
+
+def make_gatuzen(cfg, seed=0, fast=False):
+    """Random weights under the checkpoint's tensor names: bfloat16 (`_lib.BF16`-tagged bit patterns), the expert tables as float32 integers."""
+    rng = np.random.default_rng(seed)
+    w = {}
+
+    def rnd(*shape, std=1.0):
+        if fast:
+            a = rng.random(int(np.prod(shape)), dtype=np.float32)
+            a -= np.float32(0.5)
+            a *= np.float32(std * 3.4641016)
+        else:
+            a = rng.standard_normal(int(np.prod(shape)), dtype=np.float32) * np.float32(std)
+        return a.reshape(shape)
+
+    def put(name, a):
+        w[name] = _bf16_round(a)
+
+    def lin(name, out_f, in_f, gain=1.0):
+        put(name, rnd(out_f, in_f, std=gain / np.sqrt(in_f)))
+
+    W, V, taps = cfg["width"], cfg["vocab"], cfg.get("canon", {}).get("taps", 0)
+    put("embed", rnd(V, W))
+    lin("head", V, W)
+    put("final.norm", 1.0 + 0.2 * rnd(W))
+    if cfg.get("loop"):
+        put("loop.step", rnd(cfg["loop"]["times"], W, std=0.3))
+    for i, ly in enumerate(cfg["layers"]):
+        p, mx, t = "l%d." % i, ly["mixer"], ly["type"]
+        for nm in ("norm1", "norm1b"):
+            put(p + nm, 1.0 + 0.2 * rnd(W))
+        if taps:
+            put(p + "canon1", rnd(W, taps, std=0.4))
+        if t == "gla":
+            H, D, Dv, r = mx["heads"], mx["dim"], mx["vdim"], ly.get("_rank", 8)
+            lin(p + "mix.q", H * D, W); lin(p + "mix.k", H * D, W); lin(p + "mix.v", H * Dv, W); lin(p + "mix.g", H * Dv, W)
+            lin(p + "mix.a1", r, W); lin(p + "mix.a2", H * D, r, 2.0)
+            put(p + "mix.a2.b", 1.0 + rnd(H * D, std=1.0))
+            put(p + "mix.norm", 1.0 + 0.2 * rnd(Dv))
+            lin(p + "mix.o", W, H * Dv)
+        elif t == "mamba2":
+            H, P, N, G = mx["heads"], mx["vdim"], mx["state"], mx["groups"]
+            inner, Cc = H * P, H * P + 2 * G * N
+            lin(p + "mix.in", 2 * inner + 2 * G * N + H, W)
+            put(p + "mix.conv", rnd(Cc, mx["conv"], std=0.5)); put(p + "mix.conv.b", rnd(Cc, std=0.2))
+            put(p + "mix.dt_bias", rnd(H, std=1.0)); put(p + "mix.A_log", rnd(H, std=0.7)); put(p + "mix.D", rnd(H, std=1.0))
+            put(p + "mix.norm", 1.0 + 0.2 * rnd(inner))
+            lin(p + "mix.o", W, inner)
+        else:
+            H, D, R, Dv, rank = mx["heads"], mx["dim"], mx["rot_dim"], mx["vdim"], mx["kv_rank"]
+            lin(p + "mix.q", H * (D + R), W, 2.0); lin(p + "mix.dkv", rank + R, W, 2.0)
+            put(p + "mix.dkv.norm", 1.0 + 0.2 * rnd(rank))
+            lin(p + "mix.uk", H * D, rank, 2.0); lin(p + "mix.uv", H * Dv, rank)
+            lin(p + "mix.g", H * Dv, W); lin(p + "mix.o", W, H * Dv)
+        if ly.get("mlp"):
+            ml = ly["mlp"]
+            ff, E, top = ml["expert"]["ff"], ml["router"]["experts"], ml["router"]["top"]
+            for nm in ("norm2", "norm2b"):
+                put(p + nm, 1.0 + 0.2 * rnd(W))
+            if taps:
+                put(p + "canon2", rnd(W, taps, std=0.4))
+            for e in range(E):
+                q = p + "mlp.e%d." % e
+                lin(q + "gate", ff, W); lin(q + "up", ff, W); lin(q + "down", W, ff)
+            tb = np.stack([rng.permutation(E)[:top] for _ in range(V)]).astype(np.float32)
+            w[p + "mlp.table"] = tb
+    return w
