@@ -213,10 +213,12 @@ class Gatuzen:
     def new_state(self):
         return {"pos": 0, "runs": [dict() for _ in self.runs]}
 
-    def forward(self, tokens, state, trace=None):
-        """tokens [T] of ONE sequence, appended to what `state` holds.  Returns logits [T, vocab] (float64).
+    def forward(self, tokens, state=None, trace=None):
+        """tokens [T] of ONE sequence, appended to what `state` holds (None: a new sequence).  Returns logits [T, vocab] (float64).
         trace: a list that receives the stream after every layer run."""
         cfg, w = self.cfg, self.w
+        if state is None:
+            state = self.new_state()
         tokens = np.asarray(tokens, np.int64)
         x = w["embed"][tokens] * float(cfg.get("embedding", {}).get("scale", 1.0))
         pos0 = state["pos"]
@@ -248,3 +250,13 @@ class Gatuzen:
         state["pos"] = pos0 + len(tokens)
         x = group_norm(x, w["final.norm"], self.groups, self.eps)
         return (x @ w["head"].T) * float(cfg.get("logit_scale", 1.0))
+
+    def greedy(self, prompt, n):
+        """n tokens of greedy decoding after `prompt` (the first of equal maxima wins)."""
+        st = self.new_state()
+        lg = self.forward(prompt, st)[-1]
+        out = []
+        for _ in range(n):
+            out.append(int(np.argmax(lg.astype(np.float32))))
+            lg = self.forward([out[-1]], st)[-1]
+        return out
