@@ -87,3 +87,237 @@ static __global__ void latent_prep_kernel(LatentPrepArgs a) {
 }
 
 }  // namespace aha
+
+namespace aha {
+
+// ---------------------------------------------------------------------------------------------------------------------------------
+// Prompt portions.  The absorbed form costs (2 rank + R) multiply-adds per (query, key, head); with the keys and values of the
+// sequence expanded once per portion (one matrix product of its cached latents with [W_uk; W_uv], on the tensor cores in serving mode)
+// a pair costs D + R + Dv, a third of that for the usual sizes, and a head's keys are contiguous rows.  So an entry of many tokens runs
+//   latent_gather_kernel   the sequence's cached rows [latent | rotated key part], positions 0 .. S - 1, from its pages into a dense buffer
+//   (Linear)               kv[s] = [W_uk; W_uv] latent[s]
+//   latent_flash_kernel    causal softmax attention per head, fp32 on the CUDA cores, never materialising n x S: a block owns 64 queries
+//                          of one head and walks the keys in tiles of 64; thread (ty, tx) of 16 x 16 holds the scores of queries
+//                          4 ty .. 4 ty + 3 against keys tx + 16 i, then the outputs of the same queries in columns tx + 16 j, so the
+//                          running maximum and sum of a query never leave its threads (the 16 threads of a row meet by shuffles)
+// while decoded tokens and short portions stay on the absorbed form above.
+static __global__ void latent_gather_kernel(PagedKV kv, const int* __restrict__ page_table, float* __restrict__ out, int S) {
+    const int s = blockIdx.x;
+    if (s >= S) return;
+    const float* row = kv.k_row(page_table[s >> kPageShift], 0, s & (kPage - 1));
+    for (int i = threadIdx.x; i < kv.D; i += blockDim.x) out[(size_t)s * kv.D + i] = row[i];
+}
+
+struct LatentFlashArgs {
+    const float* q_plain; int ld_qp; int qp_head_stride;   // [T, .]: head h's unrotated query part at column h * qp_head_stride
+    const float* q_rot; int ld_qr; int qr_head_stride;     // [T, .]: head h's rotated part at column h * qr_head_stride
+    const float* kx; int ld_k; int k_head_stride;          // [S, .] expanded keys (unrotated part), head h at column h * k_head_stride
+    const float* vx; int ld_v; int v_head_stride;          // [S, .] expanded values
+    const float* k_rot; int ld_kr;                         // [S, .] rotated key part shared by the heads
+    float* out; int ld_o;                                  // [T, H * Dv]
+    int t0, n, pos0;                                       // the entry's packed rows t0 .. t0 + n - 1 are positions pos0 .. pos0 + n - 1
+    int D, R, Dv;
+    float scale;
+};
+
+constexpr int kLfBQ = 64, kLfBK = 64, kLfThreads = 256;
+
+__device__ __forceinline__ void lf_cp16(float* dst, const float* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void lf_cp4(float* dst, const float* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+
+// Key and value tiles come in by cp.async, all of a tile's copies in flight at once, in two groups that alternate: the next key tile is
+// requested as soon as the scores of this one are formed (it arrives under the value pass), the next value tile after the value pass (it
+// arrives under the next scores), so one buffer each is enough.  vec: every row piece is 16-byte aligned (sizes and strides multiples of 4).
+template <int NV>      // value columns per thread: Dv <= 16 NV
+static __global__ void __launch_bounds__(kLfThreads) latent_flash_kernel(LatentFlashArgs a, int vec) {
+    extern __shared__ __align__(16) float lf_sm[];
+    const int Dq = a.D + a.R, ldq = (Dq + 3) / 4 * 4 + 4, ldv = (a.Dv + 3) / 4 * 4;     // (ldq: the 16 threads of a row read different banks when Dq % 8 == 0)
+    float* Qs = lf_sm;                          // [64][ldq], scaled
+    float* Ks = Qs + kLfBQ * ldq;               // [64][ldq]
+    float* Vs = Ks + kLfBK * ldq;               // [64][ldv]
+    float* Ps = Vs + kLfBK * ldv;               // [64][64 + 4]
+    constexpr int ldp = kLfBK + 4;
+    const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4, h = blockIdx.y;
+    const int q0 = ((int)gridDim.x - 1 - (int)blockIdx.x) * kLfBQ, nq = min(kLfBQ, a.n - q0);      // the tiles with the most keys start first
+    const int last_pos = a.pos0 + q0 + nq - 1;                 // the tile's last query sees keys 0 .. last_pos
+    auto load_k = [&](int k0) {
+        const int nk = min(kLfBK, last_pos + 1 - k0);
+        if (nk > 0) {
+            if (vec) {
+                const int D4 = a.D >> 2, C4 = Dq >> 2;
+                for (int idx = tid; idx < nk * C4; idx += kLfThreads) {
+                    const int r = idx / C4, c = idx % C4;
+                    const size_t sr = (size_t)(k0 + r);
+                    lf_cp16(Ks + r * ldq + 4 * c, c < D4 ? a.kx + sr * a.ld_k + (size_t)h * a.k_head_stride + 4 * c : a.k_rot + sr * a.ld_kr + 4 * (c - D4));
+                }
+            } else {
+                for (int idx = tid; idx < nk * Dq; idx += kLfThreads) {
+                    const int r = idx / Dq, d = idx % Dq;
+                    const size_t sr = (size_t)(k0 + r);
+                    lf_cp4(Ks + r * ldq + d, d < a.D ? a.kx + sr * a.ld_k + (size_t)h * a.k_head_stride + d : a.k_rot + sr * a.ld_kr + d - a.D);
+                }
+            }
+            for (int idx = tid; idx < (kLfBK - nk) * ldq; idx += kLfThreads) Ks[nk * ldq + idx] = 0.f;     // rows past the last key
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    auto load_v = [&](int k0) {
+        const int nk = min(kLfBK, last_pos + 1 - k0);
+        if (nk > 0) {
+            if (vec) {
+                const int C4 = a.Dv >> 2;
+                for (int idx = tid; idx < nk * C4; idx += kLfThreads) {
+                    const int r = idx / C4, c = idx % C4;
+                    lf_cp16(Vs + r * ldv + 4 * c, a.vx + (size_t)(k0 + r) * a.ld_v + (size_t)h * a.v_head_stride + 4 * c);
+                }
+            } else {
+                for (int idx = tid; idx < nk * a.Dv; idx += kLfThreads) {
+                    const int r = idx / a.Dv, c = idx % a.Dv;
+                    lf_cp4(Vs + r * ldv + c, a.vx + (size_t)(k0 + r) * a.ld_v + (size_t)h * a.v_head_stride + c);
+                }
+            }
+            for (int idx = tid; idx < (kLfBK - nk) * ldv; idx += kLfThreads) Vs[nk * ldv + idx] = 0.f;     // a weight of zero must meet a finite value
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    load_k(0);
+    load_v(0);
+    for (int idx = tid; idx < kLfBQ * ldq; idx += kLfThreads) {
+        const int r = idx / ldq, d = idx % ldq;
+        float v = 0.f;
+        if (r < nq && d < Dq) {
+            const size_t t = (size_t)(a.t0 + q0 + r);
+            v = (d < a.D ? a.q_plain[t * a.ld_qp + (size_t)h * a.qp_head_stride + d] : a.q_rot[t * a.ld_qr + (size_t)h * a.qr_head_stride + d - a.D]) * a.scale;
+        }
+        Qs[idx] = v;
+        if (d >= Dq) Ks[idx] = 0.f;             // the padding columns of the key rows are never copied to
+    }
+    float m[4], l[4], o[4][NV];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        m[i] = -INFINITY; l[i] = 0.f;
+#pragma unroll
+        for (int j = 0; j < NV; ++j) o[i][j] = 0.f;
+    }
+    for (int k0 = 0; k0 <= last_pos; k0 += kLfBK) {
+        const int nk = min(kLfBK, last_pos + 1 - k0);
+        asm volatile("cp.async.wait_group 1;" ::: "memory");      // this tile's keys (its values may still be on their way)
+        __syncthreads();
+        // scores of queries 4 ty + i against keys tx + 16 u
+        float s[4][4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+            for (int u = 0; u < 4; ++u) s[i][u] = 0.f;
+        for (int d = 0; d < ldq - 4; d += 4) {
+            float4 qv[4], kv[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) qv[i] = *reinterpret_cast<const float4*>(Qs + (4 * ty + i) * ldq + d);
+#pragma unroll
+            for (int u = 0; u < 4; ++u) kv[u] = *reinterpret_cast<const float4*>(Ks + (tx + 16 * u) * ldq + d);
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int u = 0; u < 4; ++u)
+                    s[i][u] = fmaf(qv[i].w, kv[u].w, fmaf(qv[i].z, kv[u].z, fmaf(qv[i].y, kv[u].y, fmaf(qv[i].x, kv[u].x, s[i][u]))));
+        }
+        __syncthreads();                                           // every thread has read the key tile: the next one may come in
+        load_k(k0 + kLfBK);
+        // causal mask, running softmax of each query row (its 16 threads are the lanes of one half warp)
+        float corr[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int qpos = a.pos0 + q0 + 4 * ty + i;
+            float mx = -INFINITY;
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int j = k0 + tx + 16 * u;
+                if (j > qpos || tx + 16 * u >= nk) s[i][u] = -INFINITY;
+                mx = fmaxf(mx, s[i][u]);
+            }
+#pragma unroll
+            for (int off = 8; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+            const float m_new = fmaxf(m[i], mx);
+            float ps = 0.f;
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const float p = m_new == -INFINITY ? 0.f : expf(s[i][u] - m_new);     // a row of a partial tile may see no key at all
+                Ps[(4 * ty + i) * ldp + tx + 16 * u] = p;
+                ps += p;
+            }
+#pragma unroll
+            for (int off = 8; off > 0; off >>= 1) ps += __shfl_xor_sync(0xffffffffu, ps, off);
+            corr[i] = m_new == -INFINITY ? 1.f : expf(m[i] - m_new);
+            l[i] = l[i] * corr[i] + ps;
+            m[i] = m_new;
+        }
+        asm volatile("cp.async.wait_group 1;" ::: "memory");      // this tile's values (the next keys may still be on their way)
+        __syncthreads();                                           // ... and the weights are in shared memory
+        // outputs of the same queries, columns tx + 16 j
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+            for (int j = 0; j < NV; ++j) o[i][j] *= corr[i];
+        for (int k = 0; k < nk; k += 4) {
+            float4 pv[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) pv[i] = *reinterpret_cast<const float4*>(Ps + (4 * ty + i) * ldp + k);
+#pragma unroll
+            for (int kk = 0; kk < 4; ++kk) {
+                float vv[NV];
+#pragma unroll
+                for (int j = 0; j < NV; ++j) vv[j] = (tx + 16 * j < a.Dv) ? Vs[(k + kk) * ldv + tx + 16 * j] : 0.f;
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const float p = kk == 0 ? pv[i].x : (kk == 1 ? pv[i].y : (kk == 2 ? pv[i].z : pv[i].w));
+#pragma unroll
+                    for (int j = 0; j < NV; ++j) o[i][j] = fmaf(p, vv[j], o[i][j]);
+                }
+            }
+        }
+        __syncthreads();                                           // every thread has read the values and the weights
+        load_v(k0 + kLfBK);
+    }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int r = 4 * ty + i;
+        if (r >= nq) continue;
+        const float inv = 1.0f / l[i];
+        float* orow = a.out + (size_t)(a.t0 + q0 + r) * a.ld_o + (size_t)h * a.Dv;
+#pragma unroll
+        for (int j = 0; j < NV; ++j)
+            if (tx + 16 * j < a.Dv) orow[tx + 16 * j] = o[i][j] * inv;
+    }
+}
+
+inline size_t latent_flash_smem(int D, int R, int Dv) {
+    const int ldq = (D + R + 3) / 4 * 4 + 4;
+    return ((size_t)(kLfBQ + kLfBK) * ldq + (size_t)kLfBK * ((Dv + 3) / 4 * 4) + (size_t)kLfBQ * (kLfBK + 4)) * sizeof(float);
+}
+inline bool latent_flash_supported(int D, int R, int Dv) { return Dv <= 256 && latent_flash_smem(D, R, Dv) <= 200 * 1024; }
+
+inline void latent_flash(cudaStream_t st, const LatentFlashArgs& a, int H) {
+    const size_t smem = latent_flash_smem(a.D, a.R, a.Dv);
+    const dim3 grid(ceil_div(a.n, kLfBQ), H);
+    static bool attr = false;
+    if (!attr) {
+        AHA_CUDA_CHECK(cudaFuncSetAttribute(latent_flash_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        AHA_CUDA_CHECK(cudaFuncSetAttribute(latent_flash_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        AHA_CUDA_CHECK(cudaFuncSetAttribute(latent_flash_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        attr = true;
+    }
+    auto al = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+    const int vec = (a.D % 4 == 0 && a.R % 4 == 0 && a.Dv % 4 == 0 && a.ld_k % 4 == 0 && a.k_head_stride % 4 == 0 && a.ld_v % 4 == 0 && a.v_head_stride % 4 == 0 &&
+                     a.ld_kr % 4 == 0 && al(a.kx) && al(a.vx) && al(a.k_rot)) ? 1 : 0;
+    if (a.Dv <= 64) latent_flash_kernel<4><<<grid, kLfThreads, smem, st>>>(a, vec);
+    else if (a.Dv <= 128) latent_flash_kernel<8><<<grid, kLfThreads, smem, st>>>(a, vec);
+    else latent_flash_kernel<16><<<grid, kLfThreads, smem, st>>>(a, vec);
+    AHA_CUDA_CHECK(cudaGetLastError());
+}
+
+}  // namespace aha

@@ -149,6 +149,25 @@ static __global__ void split_f32_to_bf16x2_kernel(const float* __restrict__ a, i
     *reinterpret_cast<uint2*>(lo + r * K + c) = make_uint2(*reinterpret_cast<uint32_t*>(&l[0]), *reinterpret_cast<uint32_t*>(&l[2]));
 }
 
+// ... of gathered rows: output row r is input row rows[r] (the rows of a grouped product, ordered by group)
+static __global__ void gather_split_f32_to_bf16x2_kernel(const float* __restrict__ a, int lda, const int* __restrict__ rows, __nv_bfloat16* __restrict__ hi,
+                                                         __nv_bfloat16* __restrict__ lo, int M, int K) {
+    const size_t i4 = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t per_row = K / 4;
+    if (i4 >= (size_t)M * per_row) return;
+    const size_t r = i4 / per_row, c = (i4 % per_row) * 4;
+    const float4 v = *reinterpret_cast<const float4*>(a + (size_t)rows[r] * lda + c);
+    const float x[4] = {v.x, v.y, v.z, v.w};
+    __nv_bfloat16 h[4], l[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+        h[e] = __float2bfloat16_rn(x[e]);
+        l[e] = __float2bfloat16_rn(x[e] - __bfloat162float(h[e]));
+    }
+    *reinterpret_cast<uint2*>(hi + r * K + c) = make_uint2(*reinterpret_cast<uint32_t*>(&h[0]), *reinterpret_cast<uint32_t*>(&h[2]));
+    *reinterpret_cast<uint2*>(lo + r * K + c) = make_uint2(*reinterpret_cast<uint32_t*>(&l[0]), *reinterpret_cast<uint32_t*>(&l[2]));
+}
+
 // ------------------------------------------------------------------------------------------------ the GEMM kernel
 struct GemmTcArgs {
     const float* bias;
@@ -162,6 +181,11 @@ struct GemmTcArgs {
     int bf16 = 0;      // 1: A (hi / lo) and W hold bfloat16 instead of fp16 (same tiles and pipeline, the instruction descriptor names the format)
     float act_a = 0.f, act_b = 0.f;   // ACT_XIELU: alpha_p, alpha_n
     int group_m = 8;   // persistent kernel: tiles are walked in bands of group_m row blocks (n outer, m inner) so that one wave of CTAs shares few A and W tiles
+    // Grouped mode (gemm_tc_kernel only): the rows of A and C are cut into `groups` consecutive ranges by grp_offsets (device, [groups + 1]);
+    // range e multiplies with rows [e N, (e + 1) N) of the stacked weight matrix the W descriptor covers.  blockIdx.y walks the ranges' row
+    // tiles, range by range (at most ceil(M / 128) + groups of them; a block beyond the last tile leaves at once).
+    const int* grp_offsets = nullptr;
+    int groups = 0;
 };
 
 // 8 floats -> 8 fp16 hi + 8 fp16 lo (one 16-byte store each)
@@ -224,7 +248,7 @@ __device__ __forceinline__ void tc_epilogue_store(const GemmTcArgs& g, float (&v
 
 template <int EPI>
 __global__ void __launch_bounds__(kTcThreads, kTcCtasPerSm) gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_hi, const __grid_constant__ CUtensorMap tm_lo,
-                                                               const __grid_constant__ CUtensorMap tm_w, GemmTcArgs g) {
+                                                               const __grid_constant__ CUtensorMap tm_w, GemmTcArgs g_in) {
     extern __shared__ __align__(1024) uint8_t tc_smem_raw[];
     // SWIZZLE_128B tiles need 1024-byte alignment in the shared window: align by hand (1 KB of slack is allocated)
     uint8_t* tiles = tc_smem_raw + ((1024u - (smem_u32(tc_smem_raw) & 1023u)) & 1023u);   // [stages][A_hi | A_lo | W]
@@ -233,8 +257,22 @@ __global__ void __launch_bounds__(kTcThreads, kTcCtasPerSm) gemm_tc_kernel(const
     uint64_t* acc_full = empty + kTcStages;
     uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(acc_full + 1);
 
+    GemmTcArgs g = g_in;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int m0 = blockIdx.y * kTcBM, n0 = blockIdx.x * kTcBN;
+    int m0 = blockIdx.y * kTcBM;
+    const int n0 = blockIdx.x * kTcBN;
+    int w_row0 = n0;                 // first row of the W tile in the (stacked) weight matrix
+    if (g.grp_offsets) {             // the block's row tile: which range, which rows; the range's end bounds the rows that are stored
+        int slot = blockIdx.y, e = 0;
+        bool found = false;
+        for (; e < g.groups; ++e) {
+            const int r0 = g.grp_offsets[e], cnt = g.grp_offsets[e + 1] - r0, nt = (cnt + kTcBM - 1) / kTcBM;
+            if (slot < nt) { m0 = r0 + slot * kTcBM; g.M = r0 + cnt; found = true; break; }
+            slot -= nt;
+        }
+        if (!found) return;          // (all threads, before any barrier or allocation)
+        w_row0 = e * g.N + n0;
+    }
     const int nkb = g.K / kTcBK;
 
     if (tid == 0) {
@@ -261,7 +299,7 @@ __global__ void __launch_bounds__(kTcThreads, kTcCtasPerSm) gemm_tc_kernel(const
                 mbar_expect_tx(&full[s], kTcStageBytes);
                 tma_load_2d(st, &tm_hi, kb * kTcBK, m0, &full[s]);
                 tma_load_2d(st + kTcTileBytes, &tm_lo, kb * kTcBK, m0, &full[s]);
-                tma_load_2d(st + 2 * kTcTileBytes, &tm_w, kb * kTcBK, n0, &full[s]);
+                tma_load_2d(st + 2 * kTcTileBytes, &tm_w, kb * kTcBK, w_row0, &full[s]);
             }
         }
     } else if (warp == 1) {
@@ -637,6 +675,19 @@ inline void gemm_tc_launch(cudaStream_t st, int epi, const __half* a_hi, const _
         default: AHA_REQUIRE(false, "gemm_tc: bad epilogue");
     }
 #undef AHA_TC_CASE
+    AHA_CUDA_CHECK(cudaGetLastError());
+}
+
+// Grouped launch: A (hi / lo halves, [M, K]) and C rows in g.groups consecutive ranges (g.grp_offsets on the device), tm_w over the stacked
+// [groups * N, K] weights.  The grid covers the worst case of row tiles; the 128 x 128 kernel only.
+inline void gemm_tc_grouped_launch(cudaStream_t st, int epi, const __half* a_hi, const __half* a_lo, const CUtensorMap& tm_w, const GemmTcArgs& g) {
+    AHA_REQUIRE(g.grp_offsets && g.groups >= 1 && (epi == EPI_STORE || epi == EPI_SWIGLU), "gemm_tc: bad grouped launch");
+    const CUtensorMap tm_hi = make_tmap_f16(a_hi, (uint64_t)g.M, (uint64_t)g.K);
+    const CUtensorMap tm_lo = make_tmap_f16(a_lo, (uint64_t)g.M, (uint64_t)g.K);
+    const size_t smem = gemm_tc_smem_bytes();
+    dim3 grid(ceil_div(g.N, kTcBN), ceil_div(g.M, kTcBM) + g.groups);
+    if (epi == EPI_STORE) gemm_tc_kernel<EPI_STORE><<<grid, kTcThreads, smem, st>>>(tm_hi, tm_lo, tm_w, g);
+    else gemm_tc_kernel<EPI_SWIGLU><<<grid, kTcThreads, smem, st>>>(tm_hi, tm_lo, tm_w, g);
     AHA_CUDA_CHECK(cudaGetLastError());
 }
 

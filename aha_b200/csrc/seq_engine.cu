@@ -55,6 +55,7 @@ struct LinearAny {
 
 constexpr int kTcMinRows = 32;    // fewer rows than this run on the CUDA cores (a 128-row tensor-core tile would be mostly padding)
 constexpr int kGraphMaxTokens = 8;   // launches of at most this many tokens (decode steps) are replayed from CUDA graphs
+constexpr int kLatentExpandMinTokens = 32;   // a prompt portion of at least this many tokens runs latent attention over expanded keys / values
 constexpr int kTcAttnMinTokens = 32; // a prompt portion of at least this many tokens runs its attention on the tcgen05 flash kernel (serving mode, head size 64 / 128)
 
 struct Engine;
@@ -82,6 +83,10 @@ struct Sublayer {
     virtual size_t seg_decay_floats() const { return 0; }     // ... and the segments' decay products
     virtual uint64_t kv_bytes_per_token() const { return 0; }
     virtual size_t route_ints() const { return 0; }           // integer scratch of a routed feed-forward
+    virtual size_t expand_gather_floats() const { return 0; } // latent attention's prompt path: a sequence's cached rows, dense,
+    virtual size_t expand_kv_floats() const { return 0; }     // ... its expanded keys and values,
+    virtual size_t expand_out_floats() const { return 0; }    // ... the attention output of a step
+    virtual size_t expand_split_halfs() const { return 0; }   // ... and the 16-bit halves of the rows that are expanded on the tensor cores
 };
 
 struct Engine final : SeqEngine {
@@ -111,6 +116,7 @@ struct Engine final : SeqEngine {
     float* loop_step = nullptr;    // [passes, W]
     float *hnorm = nullptr, *hin = nullptr;   // [T, W] normed rows, sublayer input
     int* route_buf = nullptr;
+    float *lat_gather = nullptr, *lat_kv = nullptr, *lat_out = nullptr;   // latent attention scratch (see Sublayer::expand_*)
     // weights that several runs share are loaded once
     std::map<std::string, LinearAny> lin_cache;
     std::map<std::string, float*> vec_cache;
@@ -879,21 +885,22 @@ struct GlaMixer final : Sublayer {
     Engine& E;
     int H, D, Dv, r;
     float tau;
-    LinearAny in, a1, a2, out;
+    LinearAny in, a2, out;
     float *norm_w = nullptr, *state = nullptr;
     size_t slot_stride = 0;
-    int ld = 0, z_off = 0;
+    int ld = 0, z_off = 0, a1_off = 0;
     GlaMixer(Engine& e, const Json& mx, const WeightTable& wt, const std::string& p) : E(e) {
         H = mx.integer("heads"); D = mx.integer("dim"); Dv = mx.integer("vdim"); tau = (float)mx.number("tau");
         AHA_REQUIRE(H >= 1 && D >= 1 && Dv >= 1 && tau > 0.f, "gla: bad sizes");
         const aha_tensor_desc& d1 = wt.get(p + "a1");
         AHA_REQUIRE(d1.rank == 2, "gla: a1 must be a matrix");
         r = (int)d1.shape[0];
-        in = E.load_linear(wt, {p + "q", p + "k", p + "v", p + "g"}, {H * D, H * D, H * Dv, H * Dv}, E.W, {}, 4);
-        a1 = E.load_linear(wt, {p + "a1"}, {r}, E.W, {});
+        // the first factor of the low-rank decay projection rides along with q | k | v | g (rows padded so that the tensor-core kernels take the matrix)
+        in = E.load_linear(wt, {p + "q", p + "k", p + "v", p + "g", p + "a1"}, {H * D, H * D, H * Dv, H * Dv, r}, E.W, {}, 32);
         a2 = E.load_linear(wt, {p + "a2"}, {H * D}, r, {p + "a2.b"});
         out = E.load_linear(wt, {p + "o"}, {E.W}, H * Dv, {});
         norm_w = E.vec(wt, p + "norm", (size_t)Dv);
+        a1_off = 2 * H * D + 2 * H * Dv;
         z_off = in.N;
         ld = (in.N + H * D + 3) / 4 * 4;
         slot_stride = (size_t)H * D * Dv;
@@ -903,15 +910,14 @@ struct GlaMixer final : Sublayer {
         AHA_CUDA_CHECK(cudaFuncSetAttribute(hgrn2_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
     }
     int proj_cols() const override { return ld; }
-    int inner_cols() const override { return std::max(H * Dv, r); }
+    int inner_cols() const override { return H * Dv; }
     int max_segments() const { return E.Tmax / kSegLen + E.slots; }
     size_t seg_state_floats() const override { return E.Tmax >= kSegMinEntry ? (size_t)max_segments() * slot_stride : 0; }
     size_t seg_decay_floats() const override { return E.Tmax >= kSegMinEntry ? (size_t)max_segments() * H * D : 0; }
     void run(const StepView& v) override {
         const int T = v.rb.T, HD = H * D;
         E.gemm(AEPI_STORE, v.x, E.W, in, E.proj, ld, T);
-        E.gemm(AEPI_STORE, v.x, E.W, a1, E.inner, r, T);
-        E.gemm(AEPI_STORE, E.inner, r, a2, E.proj + z_off, ld, T);
+        E.gemm(AEPI_STORE, E.proj + a1_off, ld, a2, E.proj + z_off, ld, T);
         E.tic("linear recurrence", 4.0 * T * H * D * Dv, 4.0 * T * (3.0 * HD + 3.0 * H * Dv) + 8.0 * v.rb.E * slot_stride);
         gla_gates_kernel<<<(unsigned)(((size_t)T * HD + 255) / 256), 256, 0, E.c.stream>>>(E.proj, ld, 0, z_off, HD, 1.0f / sqrtf((float)D), 1.0f / tau, (size_t)T * HD);
         E.c.cnt.kernels++;
@@ -1004,7 +1010,8 @@ struct LatentAttentionMixer final : Sublayer {
     Engine& E;
     int H, D, R, Dv, rank;
     float scale, rot_mult = 1.f;
-    LinearAny in, out, uk_t, uv;
+    LinearAny in, out, uk_t, uv, ukv;
+    bool can_expand = false;
     int q_off = 0, dkv_off = 0, g_off = 0, n_freq = 0;
     float *c_norm = nullptr, *freq = nullptr;
     PagedKV kv;
@@ -1036,7 +1043,9 @@ struct LatentAttentionMixer final : Sublayer {
                 uk_t = E.load_rows(wt, key, src, D);
             }
             uv = E.load_linear(wt, {p + "uv"}, {H * Dv}, rank, {});
+            ukv = E.load_linear(wt, {p + "uk", p + "uv"}, {H * D, H * Dv}, rank, {}, 32);      // the prompt path expands keys and values in one product
         }
+        can_expand = E.opt.seq_impl != 1 && E.Tmax >= kLatentExpandMinTokens && latent_flash_supported(D, R, Dv);
         std::vector<float> fr;
         if (R > 0) {
             const Json& rot = mx.at("rot");
@@ -1063,6 +1072,10 @@ struct LatentAttentionMixer final : Sublayer {
     int q_cols() const override { return std::max(H * (rank + R), H * Dv); }
     size_t attn_part_floats() const override { return window_attn_part_floats(H, rank); }
     uint64_t kv_bytes_per_token() const override { return 4ull * (rank + R); }
+    size_t expand_gather_floats() const override { return can_expand ? (size_t)E.num_pages * kPage * (rank + R) : 0; }
+    size_t expand_kv_floats() const override { return can_expand ? (size_t)E.num_pages * kPage * ukv.N : 0; }
+    size_t expand_out_floats() const override { return (size_t)E.Tmax * H * Dv; }
+    size_t expand_split_halfs() const override { return can_expand && !E.fp32 ? (size_t)E.num_pages * kPage * rank : 0; }
     void run(const StepView& v) override {
         const int T = v.rb.T, ld = in.N, ldq = H * (rank + R);
         cudaStream_t st = E.c.stream;
@@ -1075,29 +1088,60 @@ struct LatentAttentionMixer final : Sublayer {
         E.c.cnt.kernels++;
         AHA_CUDA_CHECK(cudaGetLastError());
         E.toc();
-        {   // q_abs[t][h][:rank] = W_uk(h)^T q_plain[t][h]
+        // which entries are prompt portions (expanded keys / values, below) and which are served by the absorbed form
+        bool any_long = false, all_long = can_expand;
+        for (int e = 0; e < v.rb.E; ++e) {
+            const bool lg = can_expand && v.h_ent_start[e + 1] - v.h_ent_start[e] >= kLatentExpandMinTokens;
+            any_long = any_long || lg; all_long = all_long && lg;
+        }
+        float* attn_out = E.lat_out;      // [T, H * Dv]
+        if (!all_long) {   // q_abs[t][h][:rank] = W_uk(h)^T q_plain[t][h]
             GemmAnyArgs g{};
             g.A = E.proj + q_off; g.lda = ld; g.W = uk_t.w; g.C = E.qbuf; g.ldc = ldq; g.M = T; g.N = rank; g.K = D;
             g.batch = H; g.a_bs = (size_t)(D + R); g.w_bs = (size_t)rank * D; g.c_bs = (size_t)(rank + R);
             E.gemm_batched("per-head latent products", AEPI_STORE, g, 2.0 * T * H * rank * D, (double)H * rank * D * (E.fp32 ? 4 : 2) + 4.0 * T * H * (D + rank));
         }
-        WindowAttnArgs w{};
-        w.q = E.qbuf; w.kv = kv; w.slopes = nullptr; w.scale = scale; w.window = 0; w.gate = nullptr; w.out = E.inner; w.H = H; w.rb = v.rb;
-        w.part = E.opt.seq_impl == 1 ? nullptr : E.attn_part;
-        E.tic("latent attention", 2.0 * E.prof_pairs(0) * H * (2.0 * rank + R), 4.0 * (T * (double)H * (2.0 * rank + R) + E.prof_unique(0) * (rank + R)));
-        E.c.cnt.kernels += window_attn(st, w, v.span);
-        E.toc();
-        {   // o[t][h] = W_uv(h) o_latent[t][h]
+        if (!all_long) {
+            WindowAttnArgs w{};
+            w.q = E.qbuf; w.kv = kv; w.slopes = nullptr; w.scale = scale; w.window = 0; w.gate = nullptr; w.out = E.inner; w.H = H; w.rb = v.rb;
+            w.part = E.opt.seq_impl == 1 ? nullptr : E.attn_part;
+            w.skip_from_n = any_long ? kLatentExpandMinTokens : 0;
+            E.tic("latent attention (absorbed)", 2.0 * E.prof_pairs(0) * H * (2.0 * rank + R), 4.0 * (T * (double)H * (2.0 * rank + R) + E.prof_unique(0) * (rank + R)));
+            E.c.cnt.kernels += window_attn(st, w, v.span);
+            E.toc();
+            // o[t][h] = W_uv(h) o_latent[t][h]  (rows of skipped entries are overwritten below)
             GemmAnyArgs g{};
-            g.A = E.inner; g.lda = H * rank; g.W = uv.w; g.C = E.qbuf; g.ldc = H * Dv; g.M = T; g.N = Dv; g.K = rank;
+            g.A = E.inner; g.lda = H * rank; g.W = uv.w; g.C = attn_out; g.ldc = H * Dv; g.M = T; g.N = Dv; g.K = rank;
             g.batch = H; g.a_bs = (size_t)rank; g.w_bs = (size_t)Dv * rank; g.c_bs = (size_t)Dv;
             E.gemm_batched("per-head latent products", AEPI_STORE, g, 2.0 * T * H * rank * Dv, (double)H * rank * Dv * (E.fp32 ? 4 : 2) + 4.0 * T * H * (Dv + rank));
         }
+        for (int e = 0; any_long && e < v.rb.E; ++e) {
+            const int n = v.h_ent_start[e + 1] - v.h_ent_start[e], pos0 = v.h_ent_pos0[e], S = pos0 + n;
+            if (n < kLatentExpandMinTokens) continue;
+            E.tic("latent expansion (gather + linear)", 0.0, 8.0 * S * (rank + R));
+            latent_gather_kernel<<<S, 128, 0, st>>>(kv, v.rb.page_tables + (size_t)v.h_ent_slot[e] * v.rb.max_pages, E.lat_gather, S);
+            E.c.cnt.kernels++;
+            E.toc();
+            E.gemm(AEPI_STORE, E.lat_gather, rank + R, ukv, E.lat_kv, ukv.N, S);
+            LatentFlashArgs f{};
+            f.q_plain = E.proj + q_off; f.ld_qp = ld; f.qp_head_stride = D + R;
+            f.q_rot = E.qbuf + rank; f.ld_qr = ldq; f.qr_head_stride = rank + R;
+            f.kx = E.lat_kv; f.ld_k = ukv.N; f.k_head_stride = D;
+            f.vx = E.lat_kv + (size_t)H * D; f.ld_v = ukv.N; f.v_head_stride = Dv;
+            f.k_rot = E.lat_gather + rank; f.ld_kr = rank + R;
+            f.out = attn_out; f.ld_o = H * Dv; f.t0 = v.h_ent_start[e]; f.n = n; f.pos0 = pos0; f.D = D; f.R = R; f.Dv = Dv; f.scale = scale;
+            double pairs = 0;
+            for (int k = 0; k < n; ++k) pairs += pos0 + k + 1;
+            E.tic("latent attention (expanded, CUDA cores)", 2.0 * pairs * H * (D + R + Dv), 4.0 * ((double)n * H * (D + R + Dv) + (double)S * (H * (D + Dv) + R)));
+            latent_flash(st, f, H);
+            E.c.cnt.kernels++;
+            E.toc();
+        }
         E.tic("output gate", 4.0 * T * H * Dv, 12.0 * T * H * Dv);
-        gate_mul_kernel<<<(unsigned)(((size_t)T * H * Dv + 255) / 256), 256, 0, st>>>(E.qbuf, H * Dv, E.proj + g_off, ld, H * Dv, (size_t)T * H * Dv, 0);
+        gate_mul_kernel<<<(unsigned)(((size_t)T * H * Dv + 255) / 256), 256, 0, st>>>(attn_out, H * Dv, E.proj + g_off, ld, H * Dv, (size_t)T * H * Dv, 0);
         E.c.cnt.kernels++;
         E.toc();
-        E.gemm(AEPI_STORE, E.qbuf, H * Dv, out, v.y, E.W, T);
+        E.gemm(AEPI_STORE, attn_out, H * Dv, out, v.y, E.W, T);
     }
 };
 
@@ -1159,6 +1203,30 @@ struct TableMoeFF final : Sublayer {
         moe_table_route(st, r); E.c.cnt.kernels++;
         E.toc();
         const double wb = E.fp32 ? 4.0 : 2.0, used = std::min(A, experts);
+        // prompt portions in serving mode, sizes that tile: both products on the tensor cores, ONE grouped launch each over the ordered rows
+        if (!rows && !E.fp32 && E.opt.gemm_impl != 1 && T >= kTcMinRows && W % kTcBK == 0 && ff % kTcBK == 0 && W % 32 == 0) {
+            __half* hi = E.c.split_buf((size_t)A * std::max(W, ff));
+            __half* lo = hi + E.c.split_cap;
+            E.tic("expert linear (grouped, tcgen05, bf16 hi+lo)", 6.0 * A * ff * W, used * 3.0 * ff * W * wb + 4.0 * A * (3.0 * W + 3.0 * ff));
+            gather_split_f32_to_bf16x2_kernel<<<(unsigned)(((size_t)A * W / 4 + 255) / 256), 256, 0, st>>>(v.x, W, sorted_tok, reinterpret_cast<__nv_bfloat16*>(hi), reinterpret_cast<__nv_bfloat16*>(lo), A, W);
+            if (!gu.has_tmap) { gu.tmap = make_tmap_f16(gu.w, (uint64_t)gu.N, (uint64_t)gu.K); gu.has_tmap = true; }
+            if (!down.has_tmap) { down.tmap = make_tmap_f16(down.w, (uint64_t)down.N, (uint64_t)down.K); down.has_tmap = true; }
+            GemmTcArgs t{};
+            t.bias = nullptr; t.resid = nullptr; t.ldr = 0; t.C = E.proj; t.ldc = ff; t.M = A; t.N = 2 * ff; t.K = W; t.act = ACT_NONE; t.bf16 = 1;
+            t.grp_offsets = offsets; t.groups = experts;
+            gemm_tc_grouped_launch(st, EPI_SWIGLU, hi, lo, gu.tmap, t);
+            split_f32_to_bf16x2_kernel<<<(unsigned)(((size_t)A * ff / 4 + 255) / 256), 256, 0, st>>>(E.proj, ff, reinterpret_cast<__nv_bfloat16*>(hi), reinterpret_cast<__nv_bfloat16*>(lo), A, ff);
+            t.C = E.inner; t.ldc = W; t.N = W; t.K = ff;
+            gemm_tc_grouped_launch(st, EPI_STORE, hi, lo, down.tmap, t);
+            E.c.cnt.kernels += 4;
+            E.toc();
+            E.tic("expert combine", 1.0 * A * W, 4.0 * (A + T) * W);
+            moe_combine_kernel<<<(unsigned)(((size_t)T * W + 255) / 256), 256, 0, st>>>(E.inner, place_of, v.y, W, top, 1.0f / (float)top, (size_t)T * W);
+            E.c.cnt.kernels++;
+            AHA_CUDA_CHECK(cudaGetLastError());
+            E.toc();
+            return;
+        }
         GemmAnyArgs g{};
         g.A = v.x; g.lda = W; g.W = gu.w; g.C = E.proj; g.ldc = ff; g.N = 2 * ff; g.K = W; g.w_bs = (size_t)2 * ff * W;
         if (rows) { g.M = 1; g.batch = A; g.a_index = tok_of_assign; g.a_bs = (size_t)W; g.w_index = expert_of; g.c_bs = (size_t)ff; }
@@ -1302,6 +1370,17 @@ SeqEngine* make_layered_engine(Ctx& ctx, const Json& cfg, const WeightTable& wt,
     e.x = ctx.alloc<float>(T * e.W); e.y = ctx.alloc<float>(T * e.W);
     if (e.sandwich) { e.hnorm = ctx.alloc<float>(T * e.W); e.hin = ctx.alloc<float>(T * e.W); }
     if (route_ints) e.route_buf = ctx.alloc<int>(route_ints);
+    {
+        size_t ga = 0, kvf = 0, of = 0, sh = 0;
+        for (auto& ly : e.layers) {
+            ga = std::max(ga, ly.mixer->expand_gather_floats()); kvf = std::max(kvf, ly.mixer->expand_kv_floats());
+            of = std::max(of, ly.mixer->expand_out_floats()); sh = std::max(sh, ly.mixer->expand_split_halfs());
+        }
+        if (ga) e.lat_gather = ctx.alloc<float>(ga);
+        if (kvf) e.lat_kv = ctx.alloc<float>(kvf);
+        if (of) e.lat_out = ctx.alloc<float>(of);
+        if (sh) ctx.split_buf(sh);
+    }
     e.proj = ctx.alloc<float>(T * proj_cols); e.inner = ctx.alloc<float>(T * inner_cols); e.qbuf = ctx.alloc<float>(T * q_cols);
     if (!e.fp32) { gemm_tc_init(); flash_attn_tc_init(); ctx.split_buf(T * (size_t)std::max({e.W, proj_cols, inner_cols})); }
     size_t part = 0;

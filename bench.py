@@ -445,6 +445,73 @@ def bench_malasun(args):
     emit(out)
 
 
+# ------------------------------------------------------------------------------------------------- --arch gatuzen
+# width, layers (gla, mamba2 and latent-attention layers in turn, every one with experts), heads x head size, expert ff, experts / top, state, latent rank, rotated dims
+GATUZEN_SIZES = {
+    "s": dict(width=1024, n_layers=6, heads=8, head_dim=128, ff=1024, experts=8, top=2, state=64, kv_rank=256, rot_dim=64, vocab=32000),
+    "m": dict(width=2048, n_layers=6, heads=16, head_dim=128, ff=2048, experts=16, top=2, state=128, kv_rank=512, rot_dim=64, vocab=32000),
+    "l": dict(width=4096, n_layers=6, heads=32, head_dim=128, ff=2048, experts=32, top=4, state=128, kv_rank=512, rot_dim=64, vocab=32000),
+}
+
+
+def _profile_layered(m, tag, hbm, tf, W, K, n_batch=8):
+    rec = {}
+    for label, (ns, tps, ctx) in {"prefill_2048": (1, 2048, 0), "decode_b1_ctx2048": (1, 1, 2048), "decode_b%d_ctx2048" % n_batch: (n_batch, 1, 2048)}.items():
+        pr = m.seq_profile(ns, tps, ctx, W, K)
+        fam = {}
+        for k, v in pr["families"].items():
+            t = v["ms"] * 1e-3
+            roof = max(v["flops"] / (tf * 1e12), v["bytes"] / (hbm * 1e9))
+            fam[k] = {"ms": round(v["ms"], 4), "launches": v["launches"], "roofline_ms": round(roof * 1e3, 4), "of_roofline": round(roof / t, 4) if t > 0 else None,
+                      "bound": "tensor" if v["flops"] / (tf * 1e12) > v["bytes"] / (hbm * 1e9) else "HBM"}
+        rec[label] = {"tokens_per_s": round(pr["tokens_per_step"] / (pr["ms_per_step"] * 1e-3), 1), "ms_per_step": round(pr["ms_per_step"], 4),
+                      "kernels_per_step": pr["kernels_per_step"], "graph_launches_per_step": pr["graph_launches_per_step"], "families": fam}
+        log(f"[{tag}] {label}: {rec[label]['tokens_per_s']} tok/s  " + "; ".join(f"{k}: {v['ms']} ms ({v['of_roofline']})" for k, v in sorted(fam.items())))
+    return rec
+
+
+def bench_gatuzen(args):
+    """Prefill (one 2048-token prompt portion) and decode (1 and 8 sequences at context 2048) of a Gatuzen model with random weights, timed on
+    the device through the engine's own step, with the time of every kernel family against its roofline; beside it the engine's closest
+    design, Malasun, with the same width, layer count, heads and head size, and a dense feed-forward as wide as a token's active experts."""
+    from aha_b200 import B200Model, synth
+    hbm, hbm_src = measured_peaks()
+    try:
+        tf = float(json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))["bf16_tflops"])
+    except Exception:
+        tf = 1590.0
+    K, W = max(args.steps if args.steps != 128 else 16, 4), max(args.warmup, 3)
+    out = {"metric": "Gatuzen prefill / decode tokens/s beside Malasun at equal size", "unit": UNIT, "data": "synthetic", "dtype": "bf16 weights, fp32 accumulate",
+           "peaks": {"hbm_gbs": hbm, "bf16_tflops": tf, "source": hbm_src}, "prompt_tokens": 2048, "decode_ctx": 2048, "sizes": {}}
+    sampler = ClockSampler(0)
+    sampler.start()
+    for name in args.sizes.split(","):
+        sz = GATUZEN_SIZES[name]
+        cfg = synth.gatuzen_shape(**sz)
+        log(f"[gatuzen {name}] weights ...")
+        w = synth.make_gatuzen(cfg, 0, fast=True)
+        m = B200Model("gatuzen", cfg, w, max_ctx=8 * 4096, max_prefill=2048, max_seqs=8)
+        del w
+        rec = {"config": sz, "weight_bytes": m.stats()["weight_bytes"]}
+        rec.update(_profile_layered(m, "gatuzen " + name, hbm, tf, W, K))
+        m.close()
+        mc = synth.malasun_shape(width=sz["width"], n_layers=sz["n_layers"], heads=sz["heads"], kv_heads=max(1, sz["heads"] // 4), head_dim=sz["head_dim"], window=2048,
+                                 ff=sz["ff"] * sz["top"], rec_heads=sz["heads"], rec_dim=sz["head_dim"], vocab=sz["vocab"])
+        for ly in mc["layers"]:          # a feed-forward on every layer, as the Gatuzen model has
+            ly["mlp"] = {"kind": "dense", "ff": sz["ff"] * sz["top"]}
+        log(f"[malasun {name}] weights ...")
+        mw = synth.make_malasun(mc, 0, fast=True)
+        mm = B200Model("malasun", mc, mw, max_ctx=8 * 4096, max_prefill=2048, max_seqs=8)
+        del mw
+        mrec = {"weight_bytes": mm.stats()["weight_bytes"]}
+        mrec.update(_profile_layered(mm, "malasun " + name, hbm, tf, W, K))
+        mm.close()
+        rec["malasun_equal_size"] = mrec
+        out["sizes"][name] = rec
+    out["clocks"] = sampler.stop()
+    emit(out)
+
+
 def main():
     global _REAL_STDOUT
     sys.stdout.flush()
@@ -459,12 +526,14 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-tp", action="store_true", help="N > 1: skip the tensor-parallel (strong scaling) arm")
     ap.add_argument("--decode-impl", type=int, default=int(os.environ.get("AHA_DECODE_IMPL", "0")))
-    ap.add_argument("--arch", default="", help="'malasun': throughput of the layered engine's Malasun design at model-like sizes beside Qwen3 at equal "
+    ap.add_argument("--arch", default="", help="'malasun' / 'gatuzen': throughput of the layered engine's Malasun design at model-like sizes beside Qwen3 at equal "
                                                "width / depth (a separate report; the default workload and its JSON line are unchanged)")
-    ap.add_argument("--sizes", default="s,m", help="--arch malasun: which of the sizes s, m, l to run")
+    ap.add_argument("--sizes", default="s,m", help="--arch malasun / gatuzen: which of the sizes s, m, l to run")
     args = ap.parse_args()
     if args.arch == "malasun":
         return bench_malasun(args)
+    if args.arch == "gatuzen":      # the same kind of report for the Gatuzen design, beside Malasun at equal size
+        return bench_gatuzen(args)
     K, W = args.steps, max(args.warmup, 3)
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

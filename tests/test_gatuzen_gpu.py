@@ -307,6 +307,24 @@ def test_far_key_among_hundreds_and_page_borders():
     p.close()
 
 
+def test_latent_prompt_portions_of_other_head_sizes():
+    # portions of 32 tokens and more expand keys and values and run the tiled kernel (value sizes up to 64, 128 and 256 take different
+    # instances; odd sizes leave partial tiles), shorter ones and decoded tokens the absorbed form; both continue one another's cache
+    for layer in (A(heads=2, dim=20, rot_dim=6, vdim=136, kv_rank=24), A(heads=3, dim=6, rot_dim=2, vdim=5, kv_rank=9), A(heads=1, dim=40, rot_dim=24, vdim=70, kv_rank=32)):
+        p = Pair(cfg_of([layer, G()], width=32, vocab=50), seed=27, max_ctx=1024, max_seqs=3, step_tokens=512)
+        ids = p.ids(330, 3)
+        want = p.o.forward(ids)
+        p.check(p.run_cuts(ids, [70, 75, 140, 141, 205, 269, 300] + list(range(301, 330))), want, "long and short portions in turn")
+        a, b = p.ids(200, 4), p.ids(90, 5)
+        sa, sb = p.m.seq_open(), p.m.seq_open()
+        g1 = p.m.feed([(sa, a[:100], range(100)), (sb, b[:3], range(3))])
+        g2 = p.m.feed([(sb, b[3:80], range(77)), (sa, a[100:165], range(65))])          # two long entries, both continuing
+        g3 = p.m.feed([(sa, a[165:], range(35)), (sb, b[80:], range(10))])
+        p.check(np.concatenate([g1[:100], g2[77:], g3[:35]]), p.o.forward(a), "a")
+        p.check(np.concatenate([g1[100:], g2[:77], g3[35:]]), p.o.forward(b), "b")
+        p.close()
+
+
 def test_rotary_interpolation_shows_far_beyond_the_original_length():
     # positions many times the original length: a frequency table without the interpolation, or without the factor on cos / sin, gives other logits
     sc = {"factor": 8.0, "original": 16, "fast": 1.5, "slow": 0.25}      # the ramp runs from pair 1 to pair 5 of 8
