@@ -320,4 +320,154 @@ inline void latent_flash(cudaStream_t st, const LatentFlashArgs& a, int H) {
     AHA_CUDA_CHECK(cudaGetLastError());
 }
 
+// ---------------------------------------------------------------------------------------------------------------------------------
+// Decode-sized steps.  All heads of a token read the SAME cached rows, so a block owns (token, chunk of keys) for sixteen heads at a
+// time instead of one: a key row is fetched once for them.  Scores: thread (key, slice) of 32 x 8 takes every eighth 16-byte piece of the
+// key's row (the eight threads of a key read 128 consecutive bytes at a time) and holds the partial dot products of all sixteen heads,
+// summed over the slices by shuffles; softmax of a head over the tile by one warp (a lane per key); values: thread c owns latent channels
+// c and c + 256 for all sixteen heads.  Chunks are short (a few tiles) and many, so that a single decoded token still fills the GPU.  Partial results (running maximum, sum, un-normalised values per head and chunk) have the layout of
+// window_attn_kernel<true>, so window_attn_merge_kernel joins the chunks.
+constexpr int kLdThreads = 256, kLdKeys = 32, kLdHG = 16, kLdMaxSplits = 64;
+
+struct LatentDecodeArgs {
+    const float* q; int ld_q;        // [T, H * Dk] absorbed queries
+    PagedKV kv;                      // G = 1, D = Dk, Dv = rank (values alias the keys)
+    float scale;
+    float* part; int nsplit, chunk;  // see WindowAttnArgs
+    int H;
+    RaggedBatch rb;
+};
+
+static __global__ void __launch_bounds__(kLdThreads) latent_decode_attn_kernel(LatentDecodeArgs a) {
+    extern __shared__ __align__(16) float ld_sm[];
+    const int Dk = a.kv.D, Dv = a.kv.Dv;
+    float* qs = ld_sm;                          // [16][Dk], scaled
+    float* sc = qs + kLdHG * Dk;                // [16][64]
+    float* hm = sc + kLdHG * kLdKeys;           // [16] running maximum, [16] running sum, [16] rescale factor of the tile
+    float* hl = hm + kLdHG;
+    float* hc = hl + kLdHG;
+    __shared__ int pgs[kLdKeys / kPage + 2];
+    const int t = blockIdx.x, z = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int e = a.rb.tok_entry[t], i = a.rb.tok_pos[t], slot = a.rb.ent_slot[e];
+    const int* pt = a.rb.page_tables + (size_t)slot * a.rb.max_pages;
+    const int ja = z * a.chunk, jb = min(ja + a.chunk, i + 1);
+    const bool vec = (Dk & 3) == 0;
+    for (int g0 = 0; g0 < a.H; g0 += kLdHG) {
+        const int hg = min(kLdHG, a.H - g0);
+        if (ja >= jb) {                         // nothing visible in this chunk
+            if (tid < hg) { float* P = a.part + (((size_t)t * a.H + g0 + tid) * a.nsplit + z) * (size_t)(2 + Dv); P[0] = -INFINITY; P[1] = 0.f; }
+            continue;
+        }
+        for (int idx = tid; idx < hg * Dk; idx += kLdThreads) qs[idx] = a.q[(size_t)t * a.ld_q + (size_t)g0 * Dk + idx] * a.scale;
+        if (tid < kLdHG) { hm[tid] = -INFINITY; hl[tid] = 0.f; }
+        float acc[2][kLdHG];
+#pragma unroll
+        for (int r = 0; r < 2; ++r)
+#pragma unroll
+            for (int h = 0; h < kLdHG; ++h) acc[r][h] = 0.f;
+        __syncthreads();
+        for (int jt = ja; jt < jb; jt += kLdKeys) {
+            const int nj = min(kLdKeys, jb - jt), pg0 = jt >> kPageShift;
+            if (tid <= ((jt + nj - 1) >> kPageShift) - pg0) pgs[tid] = pt[pg0 + tid];
+            __syncthreads();
+            {
+                const int key = tid >> 3, ds = tid & 7;
+                float s[kLdHG];
+#pragma unroll
+                for (int h = 0; h < kLdHG; ++h) s[h] = 0.f;
+                if (key < nj) {
+                    const int j = jt + key;
+                    const float* kr = a.kv.k_row(pgs[(j >> kPageShift) - pg0], 0, j & (kPage - 1));
+                    if (vec) {
+#pragma unroll 4
+                        for (int d = 4 * ds; d < Dk; d += 32) {
+                            const float4 k4 = *reinterpret_cast<const float4*>(kr + d);
+#pragma unroll
+                            for (int h = 0; h < kLdHG; ++h) {
+                                if (h < hg) {
+                                    const float4 q4 = *reinterpret_cast<const float4*>(qs + h * Dk + d);
+                                    s[h] = fmaf(q4.w, k4.w, fmaf(q4.z, k4.z, fmaf(q4.y, k4.y, fmaf(q4.x, k4.x, s[h]))));
+                                }
+                            }
+                        }
+                    } else {
+                        for (int d = ds; d < Dk; d += 8) {
+                            const float kd = kr[d];
+#pragma unroll
+                            for (int h = 0; h < kLdHG; ++h)
+                                if (h < hg) s[h] = fmaf(qs[h * Dk + d], kd, s[h]);
+                        }
+                    }
+                }
+#pragma unroll
+                for (int h = 0; h < kLdHG; ++h) {
+                    float v = s[h];
+                    v += __shfl_xor_sync(0xffffffffu, v, 1);
+                    v += __shfl_xor_sync(0xffffffffu, v, 2);
+                    v += __shfl_xor_sync(0xffffffffu, v, 4);
+                    if (ds == 0 && h < hg) sc[h * kLdKeys + key] = key < nj ? v : -INFINITY;
+                }
+            }
+            __syncthreads();
+            for (int h = warp; h < hg; h += kLdThreads / 32) {
+                const float s0 = sc[h * kLdKeys + lane];
+                const float m_old = hm[h], m_new = fmaxf(m_old, warp_max(s0));      // every tile holds at least one visible key
+                const float p0 = expf(s0 - m_new);
+                const float ps = warp_sum(p0);
+                sc[h * kLdKeys + lane] = p0;
+                if (lane == 0) { const float c = expf(m_old - m_new); hc[h] = c; hl[h] = hl[h] * c + ps; hm[h] = m_new; }
+            }
+            __syncthreads();
+#pragma unroll
+            for (int r = 0; r < 2; ++r) {
+                const int c = tid + r * kLdThreads;
+                if (c < Dv) {
+#pragma unroll
+                    for (int h = 0; h < kLdHG; ++h) acc[r][h] *= (h < hg ? hc[h] : 0.f);
+#pragma unroll 8
+                    for (int jj = 0; jj < nj; ++jj) {
+                        const int j = jt + jj;
+                        const float v = a.kv.v_row(pgs[(j >> kPageShift) - pg0], 0, j & (kPage - 1))[c];
+#pragma unroll
+                        for (int h = 0; h < kLdHG; ++h) acc[r][h] = fmaf(h < hg ? sc[h * kLdKeys + jj] : 0.f, v, acc[r][h]);
+                    }
+                }
+            }
+            __syncthreads();       // sc, hc and pgs are rewritten by the next tile
+        }
+#pragma unroll
+        for (int h = 0; h < kLdHG; ++h) {
+            if (h < hg) {
+                float* P = a.part + (((size_t)t * a.H + g0 + h) * a.nsplit + z) * (size_t)(2 + Dv);
+                if (tid == 0) { P[0] = hm[h]; P[1] = hl[h]; }
+#pragma unroll
+                for (int r = 0; r < 2; ++r) {
+                    const int c = tid + r * kLdThreads;
+                    if (c < Dv) P[2 + c] = acc[r][h];
+                }
+            }
+        }
+        __syncthreads();           // qs, hm, hl are rewritten by the next group of heads
+    }
+}
+
+inline size_t latent_decode_smem(int Dk) { return ((size_t)kLdHG * Dk + kLdHG * kLdKeys + 3 * kLdHG) * sizeof(float); }
+inline bool latent_decode_supported(int Dk, int Dv) { return Dv <= 2 * kLdThreads && latent_decode_smem(Dk) <= 160 * 1024; }
+
+// kv_span: an upper bound of the keys any token of the step sees.  w: q, kv, scale, part, out, H, rb as for window_attn.  Returns the launches.
+inline int latent_decode_attn(cudaStream_t st, WindowAttnArgs w, int kv_span) {
+    // the partial results of T tokens fit the workspace of window_attn (kWinSplitMaxTokens tokens x kWinMaxSplits chunks)
+    w.nsplit = std::max(1, std::min({kLdMaxSplits, ceil_div(kv_span, kLdKeys), kWinSplitMaxTokens * kWinMaxSplits / std::max(1, w.rb.T)}));
+    w.chunk = ceil_div(ceil_div(kv_span, w.nsplit), kPage) * kPage;
+    w.skip_from_n = 0;
+    LatentDecodeArgs a{};
+    a.q = w.q; a.ld_q = w.H * w.kv.D; a.kv = w.kv; a.scale = w.scale; a.part = w.part; a.nsplit = w.nsplit; a.chunk = w.chunk; a.H = w.H; a.rb = w.rb;
+    static bool attr = false;
+    if (!attr) { AHA_CUDA_CHECK(cudaFuncSetAttribute(latent_decode_attn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024)); attr = true; }
+    latent_decode_attn_kernel<<<dim3(w.rb.T, w.nsplit), kLdThreads, latent_decode_smem(w.kv.D), st>>>(a);
+    window_attn_merge_kernel<<<dim3(w.rb.T, w.H), kWinAttnThreads, 0, st>>>(w);
+    AHA_CUDA_CHECK(cudaGetLastError());
+    return 2;
+}
+
 }  // namespace aha

@@ -243,19 +243,28 @@ static __global__ void __launch_bounds__(kWinAttnThreads) window_attn_kernel(Win
     }
 }
 
-// merges the chunks of a (token, head): weights exp(m_s - M) bring every partial sum to the common maximum
+// merges the chunks of a (token, head): weights exp(m_s - M) / L bring every partial sum to the common maximum.  The weights are formed
+// once (a thread per chunk), so that the sum over the chunks is a chain of multiply-adds whose loads are all in flight together.
+constexpr int kWinMergeMaxSplits = 128;
 static __global__ void __launch_bounds__(kWinAttnThreads) window_attn_merge_kernel(WindowAttnArgs a) {
-    const int t = blockIdx.x, h = blockIdx.y, Dv = a.kv.Dv;
+    __shared__ float wsm[kWinMergeMaxSplits];
+    __shared__ float red[32];
+    const int t = blockIdx.x, h = blockIdx.y, Dv = a.kv.Dv, tid = threadIdx.x;
     const float* P = a.part + ((size_t)t * a.H + h) * a.nsplit * (size_t)(2 + Dv);
-    float M = -INFINITY;
-    for (int s = 0; s < a.nsplit; ++s) M = fmaxf(M, P[(size_t)s * (2 + Dv)]);
-    float L = 0.f;
-    for (int s = 0; s < a.nsplit; ++s) { const float* ps = P + (size_t)s * (2 + Dv); if (ps[1] > 0.f) L += ps[1] * expf(ps[0] - M); }
-    const float inv = 1.0f / L;
-    for (int c = threadIdx.x; c < Dv; c += kWinAttnThreads) {
+    const bool mine = tid < a.nsplit;
+    const float ms = mine ? P[(size_t)tid * (2 + Dv)] : -INFINITY, ls = mine ? P[(size_t)tid * (2 + Dv) + 1] : 0.f;
+    const float M = block_max(ms, red);
+    const float wgt = ls > 0.f ? expf(ms - M) : 0.f;
+    const float L = block_sum(ls * wgt, red);
+    if (mine) wsm[tid] = wgt / L;
+    __syncthreads();
+    for (int c = tid; c < Dv; c += kWinAttnThreads) {
         float o = 0.f;
-        for (int s = 0; s < a.nsplit; ++s) { const float* ps = P + (size_t)s * (2 + Dv); if (ps[1] > 0.f) o = fmaf(ps[2 + c], expf(ps[0] - M), o); }
-        o *= inv;
+#pragma unroll 8
+        for (int s = 0; s < a.nsplit; ++s) {
+            const float w = wsm[s];
+            if (w != 0.f) o = fmaf(P[(size_t)s * (2 + Dv) + 2 + c], w, o);      // a chunk without visible keys left no values
+        }
         if (a.gate) o *= sigmoid_f(a.gate[(size_t)t * a.gate_ld + h * Dv + c]);
         a.out[(size_t)t * a.H * Dv + h * Dv + c] = o;
     }

@@ -21,11 +21,13 @@ struct MoeRouteArgs {
     int* place_of;       // [T * top] place of assignment a in the order   (sort)
     int* error;          // set to 1 when a table entry names no expert
     int sort;
+    int stage;           // 1: the ordering pass reads the assignments' experts from shared memory (they fit), 0: from global memory
 };
 
 static __global__ void __launch_bounds__(1024) moe_table_route_kernel(MoeRouteArgs a) {
-    extern __shared__ int cnt[];     // [experts] counts, then [experts + 1] exclusive offsets
+    extern __shared__ int cnt[];     // [experts] counts, then [experts + 1] exclusive offsets, then (stage) [T * top] experts
     const int A = a.T * a.top, tid = threadIdx.x;
+    int* eo = a.stage ? cnt + 2 * a.experts + 1 : a.expert_of;
     for (int e = tid; e < a.experts; e += blockDim.x) cnt[e] = 0;
     __syncthreads();
     for (int i = tid; i < A; i += blockDim.x) {
@@ -34,6 +36,7 @@ static __global__ void __launch_bounds__(1024) moe_table_route_kernel(MoeRouteAr
         int e = a.table[(size_t)tok * a.table_ld + i % a.top];
         if (e < 0 || e >= a.experts) { *a.error = 1; e = 0; }
         a.expert_of[i] = e;
+        if (a.stage) eo[i] = e;
         if (a.sort) atomicAdd(&cnt[e], 1);       // integer counts: the result does not depend on the order
     }
     if (!a.sort) return;
@@ -52,7 +55,7 @@ static __global__ void __launch_bounds__(1024) moe_table_route_kernel(MoeRouteAr
         int run = off[e];
         for (int i0 = 0; i0 < A; i0 += 32) {
             const int i = i0 + lane;
-            const bool mine = i < A && a.expert_of[i] == e;
+            const bool mine = i < A && eo[i] == e;
             const unsigned m = __ballot_sync(0xffffffffu, mine);
             if (mine) {
                 const int p = run + __popc(m & ((1u << lane) - 1u));
@@ -67,7 +70,11 @@ static __global__ void __launch_bounds__(1024) moe_table_route_kernel(MoeRouteAr
 inline void moe_table_route(cudaStream_t st, const MoeRouteArgs& a) {
     const int A = a.T * a.top;
     const int threads = a.sort ? 1024 : std::min(1024, std::max(32, (A + 31) / 32 * 32));
-    moe_table_route_kernel<<<1, threads, (2 * (size_t)a.experts + 1) * sizeof(int), st>>>(a);
+    MoeRouteArgs b = a;
+    size_t smem = (2 * (size_t)a.experts + 1) * sizeof(int);
+    b.stage = a.sort && smem + (size_t)A * sizeof(int) <= 48 * 1024 ? 1 : 0;
+    if (b.stage) smem += (size_t)A * sizeof(int);
+    moe_table_route_kernel<<<1, threads, smem, st>>>(b);
     AHA_CUDA_CHECK(cudaGetLastError());
 }
 

@@ -1107,7 +1107,8 @@ struct LatentAttentionMixer final : Sublayer {
             w.part = E.opt.seq_impl == 1 ? nullptr : E.attn_part;
             w.skip_from_n = any_long ? kLatentExpandMinTokens : 0;
             E.tic("latent attention (absorbed)", 2.0 * E.prof_pairs(0) * H * (2.0 * rank + R), 4.0 * (T * (double)H * (2.0 * rank + R) + E.prof_unique(0) * (rank + R)));
-            E.c.cnt.kernels += window_attn(st, w, v.span);
+            if (w.part && !any_long && T <= kWinSplitMaxTokens && latent_decode_supported(kv.D, kv.Dv)) E.c.cnt.kernels += latent_decode_attn(st, w, v.span);     // all heads share a block's key rows
+            else E.c.cnt.kernels += window_attn(st, w, v.span);
             E.toc();
             // o[t][h] = W_uv(h) o_latent[t][h]  (rows of skipped entries are overwritten below)
             GemmAnyArgs g{};
