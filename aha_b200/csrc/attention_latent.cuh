@@ -418,18 +418,20 @@ static __global__ void __launch_bounds__(kLdThreads) latent_decode_attn_kernel(L
                 if (lane == 0) { const float c = expf(m_old - m_new); hc[h] = c; hl[h] = hl[h] * c + ps; hm[h] = m_new; }
             }
             __syncthreads();
+            {
+                const int c0 = tid, c1 = tid + kLdThreads;
 #pragma unroll
-            for (int r = 0; r < 2; ++r) {
-                const int c = tid + r * kLdThreads;
-                if (c < Dv) {
-#pragma unroll
-                    for (int h = 0; h < kLdHG; ++h) acc[r][h] *= (h < hg ? hc[h] : 0.f);
+                for (int h = 0; h < kLdHG; ++h) { const float f = h < hg ? hc[h] : 0.f; acc[0][h] *= f; acc[1][h] *= f; }
 #pragma unroll 8
-                    for (int jj = 0; jj < nj; ++jj) {
-                        const int j = jt + jj;
-                        const float v = a.kv.v_row(pgs[(j >> kPageShift) - pg0], 0, j & (kPage - 1))[c];
+                for (int jj = 0; jj < nj; ++jj) {      // both columns' loads of eight keys in flight together
+                    const int j = jt + jj;
+                    const float* vr = a.kv.v_row(pgs[(j >> kPageShift) - pg0], 0, j & (kPage - 1));
+                    const float v0 = c0 < Dv ? vr[c0] : 0.f, v1 = c1 < Dv ? vr[c1] : 0.f;
 #pragma unroll
-                        for (int h = 0; h < kLdHG; ++h) acc[r][h] = fmaf(h < hg ? sc[h * kLdKeys + jj] : 0.f, v, acc[r][h]);
+                    for (int h = 0; h < kLdHG; ++h) {
+                        const float p = h < hg ? sc[h * kLdKeys + jj] : 0.f;
+                        acc[0][h] = fmaf(p, v0, acc[0][h]);
+                        acc[1][h] = fmaf(p, v1, acc[1][h]);
                     }
                 }
             }

@@ -258,15 +258,28 @@ static __global__ void __launch_bounds__(kWinAttnThreads) window_attn_merge_kern
     const float L = block_sum(ls * wgt, red);
     if (mine) wsm[tid] = wgt / L;
     __syncthreads();
-    for (int c = tid; c < Dv; c += kWinAttnThreads) {
-        float o = 0.f;
-#pragma unroll 8
-        for (int s = 0; s < a.nsplit; ++s) {
-            const float w = wsm[s];
-            if (w != 0.f) o = fmaf(P[(size_t)s * (2 + Dv) + 2 + c], w, o);      // a chunk without visible keys left no values
+    float o[kWinAttnMaxAcc];          // channels tid, tid + 128, ...: their loads of a chunk are in flight together
+#pragma unroll
+    for (int r = 0; r < kWinAttnMaxAcc; ++r) o[r] = 0.f;
+#pragma unroll 4
+    for (int s = 0; s < a.nsplit; ++s) {
+        const float w = wsm[s];
+        if (w == 0.f) continue;           // a chunk without visible keys left no values
+        const float* ps = P + (size_t)s * (2 + Dv) + 2;
+#pragma unroll
+        for (int r = 0; r < kWinAttnMaxAcc; ++r) {
+            const int c = tid + r * kWinAttnThreads;
+            if (c < Dv) o[r] = fmaf(ps[c], w, o[r]);
         }
-        if (a.gate) o *= sigmoid_f(a.gate[(size_t)t * a.gate_ld + h * Dv + c]);
-        a.out[(size_t)t * a.H * Dv + h * Dv + c] = o;
+    }
+#pragma unroll
+    for (int r = 0; r < kWinAttnMaxAcc; ++r) {
+        const int c = tid + r * kWinAttnThreads;
+        if (c < Dv) {
+            float v = o[r];
+            if (a.gate) v *= sigmoid_f(a.gate[(size_t)t * a.gate_ld + h * Dv + c]);
+            a.out[(size_t)t * a.H * Dv + h * Dv + c] = v;
+        }
     }
 }
 

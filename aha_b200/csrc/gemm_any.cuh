@@ -27,6 +27,11 @@ struct GemmAnyArgs {
     size_t a_bs = 0, w_bs = 0, c_bs = 0;
     const int* a_index = nullptr;
     const int* w_index = nullptr;
+    // ... or wi looked up on the way: wi = w_table[w_keys[b / w_div] * w_table_ld + b % w_div] (the choice b % w_div of the row whose key -- a
+    // token id -- is w_keys[b / w_div], in a table of choices per key): a routed product needs no routing launch of its own
+    const int* w_keys = nullptr;
+    const int* w_table = nullptr;
+    int w_table_ld = 0, w_div = 1;
     // row_offsets (device, [batch + 1]): batch b owns rows [ro[b], ro[b + 1]) of A and C, M is an upper bound of a batch's rows (tile kernel only)
     const int* row_offsets = nullptr;
     const int* a_gather = nullptr;   // (tile kernel only) row m of A is row a_gather[m] of the buffer: a gather folded into the load
@@ -37,7 +42,7 @@ template <typename WT>
 __device__ __forceinline__ const WT* any_batch_setup(GemmAnyArgs& g) {
     const WT* W = reinterpret_cast<const WT*>(g.W);
     const int b = blockIdx.z;
-    const int wi = g.w_index ? g.w_index[b] : b;
+    const int wi = g.w_index ? g.w_index[b] : (g.w_keys ? g.w_table[(size_t)g.w_keys[b / g.w_div] * g.w_table_ld + b % g.w_div] : b);
     W += (size_t)wi * g.w_bs;
     if (g.bias) g.bias += (size_t)wi * (g.w_bs ? g.N : 0);
     g.A += (size_t)(g.a_index ? g.a_index[b] : b) * g.a_bs;

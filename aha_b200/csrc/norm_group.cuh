@@ -27,6 +27,8 @@ struct GroupNormArgs {
     float eps;
     int C, groups;
     float* out; int ld_out;
+    int sum_rows = 1;                 // > 1: the value of row r is the sum of rows r * sum_rows .. + sum_rows - 1 of `in` (the outputs of a token's experts), times in_scale
+    float in_scale = 1.f;
     float mult = 1.f;                 // on the normed value (a residual multiplier, a logit scale)
     int add = 0;                      // 1: out += mult * normed (the residual sum), 0: out = mult * normed
 };
@@ -39,7 +41,13 @@ static __global__ void group_rmsnorm_kernel(GroupNormArgs a) {
     const float* gt = a.gate ? a.gate + src * a.ld_gate : nullptr;
     const float* sk = a.skip ? a.skip + src * a.ld_skip : nullptr;
     auto value = [&](int c) {
-        float v = x[c];
+        float v;
+        if (a.sum_rows > 1) {
+            const float* xs = a.in + src * a.sum_rows * a.ld_in;
+            v = 0.f;
+            for (int k = 0; k < a.sum_rows; ++k) v += xs[(size_t)k * a.ld_in + c];
+            v *= a.in_scale;
+        } else v = x[c];
         if (sk) v = fmaf(a.skip_w[c / a.skip_span], sk[c], v);
         if (gt) v *= silu_f(gt[c]);
         return v;

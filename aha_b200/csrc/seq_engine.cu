@@ -115,6 +115,9 @@ struct Engine final : SeqEngine {
     float* final_w = nullptr;      // sandwich: [W] gain of the final norm
     float* loop_step = nullptr;    // [passes, W]
     float *hnorm = nullptr, *hin = nullptr;   // [T, W] normed rows, sublayer input
+    // a sublayer may leave its output as `out_rows` rows per token that are still to be summed and scaled (a token's experts in decode steps):
+    // the norm + residual kernel that follows does it on the way
+    const float* out_src = nullptr; int out_rows = 1; float out_scale = 1.f;
     int* route_buf = nullptr;
     float *lat_gather = nullptr, *lat_kv = nullptr, *lat_out = nullptr;   // latent attention scratch (see Sublayer::expand_*)
     // weights that several runs share are loaded once
@@ -622,6 +625,7 @@ struct Engine final : SeqEngine {
         tic("norm + residual", 4.0 * T * W, 12.0 * T * W);
         GroupNormArgs n{};
         n.in = y; n.ld_in = W; n.w = gain; n.eps = eps; n.C = W; n.groups = norm_groups; n.out = x; n.ld_out = W; n.mult = resid_mult; n.add = 1;
+        if (out_src) { n.in = out_src; n.sum_rows = out_rows; n.in_scale = out_scale; out_src = nullptr; }
         group_rmsnorm(c.stream, n, T); c.cnt.kernels++;
         toc();
     }
@@ -1197,12 +1201,14 @@ struct TableMoeFF final : Sublayer {
         cudaStream_t st = E.c.stream;
         int* expert_of = E.route_buf; int* sorted_tok = expert_of + (size_t)E.Tmax * top; int* place_of = sorted_tok + (size_t)E.Tmax * top; int* offsets = place_of + (size_t)E.Tmax * top;
         const bool rows = T <= kGraphMaxTokens && E.opt.seq_impl != 1;      // decode-sized steps: a batch per assignment, no ordering
-        E.tic("expert routing (table)", 0.0, 16.0 * A);
-        MoeRouteArgs r{};
-        r.tokens = v.rb.tokens; r.T = T; r.table = table; r.table_ld = table_ld; r.V = E.V; r.top = top; r.experts = experts;
-        r.expert_of = expert_of; r.offsets = offsets; r.sorted_tok = sorted_tok; r.place_of = place_of; r.error = err; r.sort = rows ? 0 : 1;
-        moe_table_route(st, r); E.c.cnt.kernels++;
-        E.toc();
+        if (!rows) {      // (decode-sized steps look the experts up inside the products)
+            E.tic("expert routing (table)", 0.0, 16.0 * A);
+            MoeRouteArgs r{};
+            r.tokens = v.rb.tokens; r.T = T; r.table = table; r.table_ld = table_ld; r.V = E.V; r.top = top; r.experts = experts;
+            r.expert_of = expert_of; r.offsets = offsets; r.sorted_tok = sorted_tok; r.place_of = place_of; r.error = err; r.sort = 1;
+            moe_table_route(st, r); E.c.cnt.kernels++;
+            E.toc();
+        }
         const double wb = E.fp32 ? 4.0 : 2.0, used = std::min(A, experts);
         // prompt portions in serving mode, sizes that tile: both products on the tensor cores, ONE grouped launch each over the ordered rows
         if (!rows && !E.fp32 && E.opt.gemm_impl != 1 && T >= kTcMinRows && W % kTcBK == 0 && ff % kTcBK == 0 && W % 32 == 0) {
@@ -1230,14 +1236,21 @@ struct TableMoeFF final : Sublayer {
         }
         GemmAnyArgs g{};
         g.A = v.x; g.lda = W; g.W = gu.w; g.C = E.proj; g.ldc = ff; g.N = 2 * ff; g.K = W; g.w_bs = (size_t)2 * ff * W;
-        if (rows) { g.M = 1; g.batch = A; g.a_index = tok_of_assign; g.a_bs = (size_t)W; g.w_index = expert_of; g.c_bs = (size_t)ff; }
+        if (rows) {
+            g.M = 1; g.batch = A; g.a_index = tok_of_assign; g.a_bs = (size_t)W; g.c_bs = (size_t)ff;
+            g.w_keys = reinterpret_cast<const int*>(v.rb.tokens); g.w_table = table; g.w_table_ld = table_ld; g.w_div = top;
+        }
         else { g.M = A; g.batch = experts; g.row_offsets = offsets; g.a_gather = sorted_tok; }
         E.gemm_batched(rows ? "expert linear (decode rows)" : "expert linear (grouped, CUDA cores)", AEPI_SWIGLU, g, 4.0 * A * ff * W, used * 2.0 * ff * W * wb + 4.0 * A * (W + ff));
         GemmAnyArgs d{};
         d.A = E.proj; d.lda = ff; d.W = down.w; d.C = E.inner; d.ldc = W; d.N = W; d.K = ff; d.w_bs = (size_t)W * ff;
-        if (rows) { d.M = 1; d.batch = A; d.a_bs = (size_t)ff; d.w_index = expert_of; d.c_bs = (size_t)W; }
+        if (rows) {
+            d.M = 1; d.batch = A; d.a_bs = (size_t)ff; d.c_bs = (size_t)W;
+            d.w_keys = reinterpret_cast<const int*>(v.rb.tokens); d.w_table = table; d.w_table_ld = table_ld; d.w_div = top;
+        }
         else { d.M = A; d.batch = experts; d.row_offsets = offsets; }
         E.gemm_batched(rows ? "expert linear (decode rows)" : "expert linear (grouped, CUDA cores)", AEPI_STORE, d, 2.0 * A * ff * W, used * ff * W * wb + 4.0 * A * (W + ff));
+        if (rows && E.sandwich) { E.out_src = E.inner; E.out_rows = top; E.out_scale = 1.0f / (float)top; return; }     // summed by the norm + residual kernel
         E.tic("expert combine", 1.0 * A * W, 4.0 * (A + T) * W);
         moe_combine_kernel<<<(unsigned)(((size_t)T * W + 255) / 256), 256, 0, st>>>(E.inner, rows ? nullptr : place_of, v.y, W, top, 1.0f / (float)top, (size_t)T * W);
         E.c.cnt.kernels++;
