@@ -310,7 +310,9 @@ def test_far_key_among_hundreds_and_page_borders():
 def test_latent_prompt_portions_of_other_head_sizes():
     # portions of 32 tokens and more expand keys and values and run the tiled kernel (value sizes up to 64, 128 and 256 take different
     # instances; odd sizes leave partial tiles), shorter ones and decoded tokens the absorbed form; both continue one another's cache
-    for layer in (A(heads=2, dim=20, rot_dim=6, vdim=136, kv_rank=24), A(heads=3, dim=6, rot_dim=2, vdim=5, kv_rank=9), A(heads=1, dim=40, rot_dim=24, vdim=70, kv_rank=32)):
+    # (18 heads: the decode kernel serves sixteen heads at a time, then the other two)
+    for layer in (A(heads=2, dim=20, rot_dim=6, vdim=136, kv_rank=24), A(heads=3, dim=6, rot_dim=2, vdim=5, kv_rank=9), A(heads=1, dim=40, rot_dim=24, vdim=70, kv_rank=32),
+                  A(heads=18, dim=8, rot_dim=4, vdim=8, kv_rank=20)):
         p = Pair(cfg_of([layer, G()], width=32, vocab=50), seed=27, max_ctx=1024, max_seqs=3, step_tokens=512)
         ids = p.ids(330, 3)
         want = p.o.forward(ids)
