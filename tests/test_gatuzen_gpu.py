@@ -327,6 +327,45 @@ def test_latent_prompt_portions_of_other_head_sizes():
         p.close()
 
 
+@pytest.mark.parametrize("seed", range(14))
+def test_random_shapes_and_layer_orders(seed):
+    # sizes, head counts, layer order, loop span and constants drawn at random (odd sizes included): nothing may rest on one model's values
+    r = np.random.default_rng(100 + seed)
+    pick = lambda *xs: xs[int(r.integers(0, len(xs)))]
+    groups = pick(1, 2, 3, 4)
+    width = groups * pick(6, 10, 16, 20)
+
+    def moe():
+        n = pick(2, 3, 5, 9)
+        return pick(None, E(n, int(r.integers(1, n + 1)), pick(6, 16, 24)))
+
+    def layer():
+        t = pick("gla", "mamba2", "latent")
+        if t == "gla":
+            return G(heads=pick(1, 2, 5), dim=pick(4, 6, 16, 36), vdim=pick(4, 10, 32, 40), tau=pick(1.0, 4.0, 16.0, 64.0), rank=pick(1, 3, 8), moe=moe())
+        if t == "mamba2":
+            g = pick(1, 2, 3)
+            ng = pick(1, 2, 4)
+            return M(heads=g * pick(1, 2, 4), vdim=ng * pick(2, 3, 8), state=pick(4, 6, 16, 40), groups=g, norm_groups=ng, conv=pick(1, 2, 4, 7), moe=moe())
+        rd = pick(2, 4, 8, 12)
+        sc = pick(None, {"factor": pick(2.0, 6.0, 16.0), "original": pick(8, 32, 128), "fast": pick(2.0, 8.0, 32.0), "slow": pick(0.5, 1.0, 2.0)})
+        return A(heads=pick(1, 2, 3, 7), dim=pick(4, 6, 16, 24), rot_dim=rd, vdim=pick(4, 6, 16, 36), kv_rank=pick(4, 10, 16, 48), base=pick(10.0, 1e3, 1e6), scaling=sc,
+                 scale=pick(None, 0.2, 0.5), moe=moe())
+
+    n = int(r.integers(1, 6))
+    layers = [layer() for _ in range(n)]
+    a = int(r.integers(0, n + 1)); b = int(r.integers(a, n + 1))
+    loop = pick(None, (a, b, pick(1, 2, 3)))
+    cfg = synth.gatuzen_config(layers, width=width, vocab=pick(17, 50, 131), eps=pick(1e-6, 1e-5, 1e-3), groups=groups, taps=pick(0, 1, 2, 4, 6),
+                               residual_mult=pick(0.2, 0.5, 1.0, 1.7), embed_scale=pick(0.25, 1.0, 3.0), logit_scale=pick(0.5, 1.0, 4.0), loop=loop)
+    p = Pair(cfg, seed=seed, exact=seed % 3 != 0, max_ctx=512, max_seqs=3, step_tokens=pick(48, 200, 512))      # (every third one in serving mode)
+    ids = p.ids(170, seed)
+    want = p.o.forward(ids)
+    p.check(p.run_cuts(ids, []), want, "whole")
+    p.check(p.run_cuts(ids, [1, 3, 40, 41, 100, 133] + list(range(140, 170))), want, "portions and decoding")
+    p.close()
+
+
 def test_rotary_interpolation_shows_far_beyond_the_original_length():
     # positions many times the original length: a frequency table without the interpolation, or without the factor on cos / sin, gives other logits
     sc = {"factor": 8.0, "original": 16, "fast": 1.5, "slow": 0.25}      # the ramp runs from pair 1 to pair 5 of 8
