@@ -122,12 +122,14 @@ __device__ __forceinline__ void pack8_split(const float* p, uint4& hi, uint4& lo
     split2(p[6], p[7], hi.w, lo.w);
 }
 
-template <int HD, bool CAUSAL, bool WIN = false>
-__global__ void __launch_bounds__(kFaThreads, HD == 64 ? 2 : 1) flash_attn_tc_kernel(const __grid_constant__ CUtensorMap tm_qh, const __grid_constant__ CUtensorMap tm_ql,
+// HDQ: the size of the query / key rows when it differs from the value size HD (keys with an extra rotated part: 192 against 128); the
+// score products then walk HDQ / 16 steps over HDQ / 64 tile blocks, everything after the scores is the same.
+template <int HD, bool CAUSAL, bool WIN = false, int HDQ = HD>
+__global__ void __launch_bounds__(kFaThreads, (HD == 64 && HDQ == 64) ? 2 : 1) flash_attn_tc_kernel(const __grid_constant__ CUtensorMap tm_qh, const __grid_constant__ CUtensorMap tm_ql,
                                                                      const __grid_constant__ CUtensorMap tm_kh, const __grid_constant__ CUtensorMap tm_kl,
                                                                      const __grid_constant__ CUtensorMap tm_vh, const __grid_constant__ CUtensorMap tm_vl, FlashTcArgs a) {
-    constexpr int BQ = kFaBQ, BKV = kFaBKV, KB = HD / 64;   // KB: 64-half k-blocks per head row (one TMA box each)
-    constexpr int kQBytes = BQ * HD * 2, kKBytes = BKV * HD * 2, kVBytes = HD * BKV * 2, kPBytes = BQ * BKV * 2;   // head_dim 64: 16, 8, 8, 16 KB
+    constexpr int BQ = kFaBQ, BKV = kFaBKV, KB = HDQ / 64;   // KB: 64-half k-blocks per query / key row (one TMA box each)
+    constexpr int kQBytes = BQ * HDQ * 2, kKBytes = BKV * HDQ * 2, kVBytes = HD * BKV * 2, kPBytes = BQ * BKV * 2;   // head_dim 64: 16, 8, 8, 16 KB
     constexpr int kQBlk = BQ * 128, kKBlk = BKV * 128;       // bytes of one k-block of the Q / K tile
     extern __shared__ __align__(1024) uint8_t fa_tc_smem_raw[];
     uint8_t* base = fa_tc_smem_raw + ((1024u - (smem_u32(fa_tc_smem_raw) & 1023u)) & 1023u);
@@ -191,7 +193,7 @@ __global__ void __launch_bounds__(kFaThreads, HD == 64 ? 2 : 1) flash_attn_tc_ke
             auto issue_s = [&](int t) {                          // S(t) = Qh Kh^T + Qh Kl^T + Ql Kh^T into S buffer t & 1
                 const uint32_t dst = tmem_s + (uint32_t)((t & 1) * 64);
 #pragma unroll
-                for (int ks = 0; ks < HD / 16; ++ks) {   // k-block ks / 4 of the tiles, 32 bytes per K = 16 step inside its 128-byte swizzle atom
+                for (int ks = 0; ks < HDQ / 16; ++ks) {   // k-block ks / 4 of the tiles, 32 bytes per K = 16 step inside its 128-byte swizzle atom
                     const uint64_t qa = (uint64_t)(((ks >> 2) * kQBlk + (ks & 3) * 32) >> 4), ka = (uint64_t)(((ks >> 2) * kKBlk + (ks & 3) * 32) >> 4);
                     umma_f16(dst, d_qh + qa, d_kh + ka, idesc, ks > 0 ? 1u : 0u);
                     umma_f16(dst, d_qh + qa, d_kl + ka, idesc, 1u);
@@ -384,8 +386,8 @@ __global__ void __launch_bounds__(kFaThreads, HD == 64 ? 2 : 1) flash_attn_tc_ke
     }
 }
 
-template <int HD>
-inline size_t flash_tc_smem_bytes() { return (size_t)(2 * kFaBQ * HD * 2 + 2 * kFaBKV * HD * 2 + 2 * HD * kFaBKV * 2 + 2 * kFaBQ * kFaBKV * 2) + 8 * sizeof(uint64_t) + 1024; }
+template <int HD, int HDQ = HD>
+inline size_t flash_tc_smem_bytes() { return (size_t)(2 * kFaBQ * HDQ * 2 + 2 * kFaBKV * HDQ * 2 + 2 * HD * kFaBKV * 2 + 2 * kFaBQ * kFaBKV * 2) + 8 * sizeof(uint64_t) + 1024; }
 inline int flash_tc_skv_pad(int Skv) { return ceil_div(Skv, 64) * 64; }
 // workspace halfs: q hi|lo + k hi|lo ([head][token][HD]) + v^T hi|lo ([head][HD][skv_pad])
 template <int HD>
@@ -400,6 +402,8 @@ inline void flash_attn_tc_init() {
     AHA_CUDA_CHECK(cudaFuncSetAttribute(flash_attn_tc_kernel<128, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)flash_tc_smem_bytes<128>()));
     AHA_CUDA_CHECK(cudaFuncSetAttribute(flash_attn_tc_kernel<64, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)flash_tc_smem_bytes<64>()));
     AHA_CUDA_CHECK(cudaFuncSetAttribute(flash_attn_tc_kernel<128, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)flash_tc_smem_bytes<128>()));
+    AHA_CUDA_CHECK(cudaFuncSetAttribute(flash_attn_tc_kernel<128, true, false, 192>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)flash_tc_smem_bytes<128, 192>()));
+    AHA_CUDA_CHECK(cudaFuncSetAttribute(flash_attn_tc_kernel<64, true, false, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)flash_tc_smem_bytes<64, 128>()));
 }
 struct FlashWindow {        // what the WIN kernels add to causal attention; window 0, no slopes and no gate is plain causal attention
     int window = 0;

@@ -26,7 +26,7 @@
 #include <functional>
 #include <memory>
 
-#include "attention_latent.cuh"
+#include "attention_latent_tc.cuh"
 #include "attention_tc.cuh"
 #include "attention_window.cuh"
 #include "gemm_any.cuh"
@@ -1079,7 +1079,14 @@ struct LatentAttentionMixer final : Sublayer {
     size_t expand_gather_floats() const override { return can_expand ? (size_t)E.num_pages * kPage * (rank + R) : 0; }
     size_t expand_kv_floats() const override { return can_expand ? (size_t)E.num_pages * kPage * ukv.N : 0; }
     size_t expand_out_floats() const override { return (size_t)E.Tmax * H * Dv; }
-    size_t expand_split_halfs() const override { return can_expand && !E.fp32 ? (size_t)E.num_pages * kPage * rank : 0; }
+    bool expand_on_tc() const { return can_expand && !E.fp32 && latent_flash_tc_supported(D, R, Dv); }
+    size_t expand_split_halfs() const override {
+        if (!can_expand || E.fp32) return 0;
+        const size_t smax = (size_t)E.num_pages * kPage;
+        size_t h = smax * rank;                                               // the expansion product's activations
+        if (expand_on_tc()) h = std::max(h, latent_flash_tc_ws_halfs(H, E.Tmax, (int)smax, D, R, Dv) / 2);    // the packed q, k, v^T of the longest entry
+        return h;
+    }
     void run(const StepView& v) override {
         const int T = v.rb.T, ld = in.N, ldq = H * (rank + R);
         cudaStream_t st = E.c.stream;
@@ -1137,9 +1144,14 @@ struct LatentAttentionMixer final : Sublayer {
             f.out = attn_out; f.ld_o = H * Dv; f.t0 = v.h_ent_start[e]; f.n = n; f.pos0 = pos0; f.D = D; f.R = R; f.Dv = Dv; f.scale = scale;
             double pairs = 0;
             for (int k = 0; k < n; ++k) pairs += pos0 + k + 1;
-            E.tic("latent attention (expanded, CUDA cores)", 2.0 * pairs * H * (D + R + Dv), 4.0 * ((double)n * H * (D + R + Dv) + (double)S * (H * (D + Dv) + R)));
-            latent_flash(st, f, H);
-            E.c.cnt.kernels++;
+            if (expand_on_tc()) {
+                E.tic("latent attention (expanded, tcgen05, split fp16)", 2.0 * pairs * H * (D + R + Dv), 4.0 * ((double)n * H * (D + R + Dv) + (double)S * (H * (D + Dv) + R)));
+                E.c.cnt.kernels += latent_flash_tc(st, f, H, E.c.split_buf((latent_flash_tc_ws_halfs(H, n, S, D, R, Dv) + 1) / 2));
+            } else {
+                E.tic("latent attention (expanded, CUDA cores)", 2.0 * pairs * H * (D + R + Dv), 4.0 * ((double)n * H * (D + R + Dv) + (double)S * (H * (D + Dv) + R)));
+                latent_flash(st, f, H);
+                E.c.cnt.kernels++;
+            }
             E.toc();
         }
         E.tic("output gate", 4.0 * T * H * Dv, 12.0 * T * H * Dv);

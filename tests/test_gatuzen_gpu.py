@@ -168,6 +168,28 @@ def test_tensor_core_linears_in_serving_mode():
     p.close()
 
 
+@pytest.mark.parametrize("dims", [(40, 8, 64), (64, 32, 64), (64, 32, 128), (128, 64, 128)])
+def test_tensor_core_latent_attention_in_serving_mode(dims):
+    # value sizes 64 and 128 with keys of up to 192 values: prompt portions of 32 tokens and more run on the tcgen05 flash kernel (key rows
+    # longer than value rows, zero-padded to a multiple of 64), shorter portions and decoded tokens on the CUDA-core kernels; the marked
+    # token's key and value stand out, so a tile that is skipped or masked wrongly moves the rows behind it far beyond the budget
+    dim, rot, vdim = dims
+    mark = 3
+    cfg = cfg_of([A(heads=3, dim=dim, rot_dim=rot, vdim=vdim, kv_rank=64, base=1e4, scaling={"factor": 2.0, "original": 128, "fast": 8.0, "slow": 1.0}, moe=E(3, 2, 64)), G(heads=2, dim=16, vdim=16)],
+                 width=64, vocab=90)
+    p = Pair(cfg, seed=31, exact=False, max_ctx=2048, step_tokens=1024, boost=mark)
+    ids = p.ids(700, 6, avoid=mark)
+    ids[[5, 200, 263, 455]] = mark
+    want = p.o.forward(ids)
+    for cuts in ([], [40, 45, 300, 333, 429, 461, 600], [130, 131, 194, 195, 259] + list(range(640, 700))):
+        got = p.run_cuts(ids, cuts)
+        err = np.abs(got - want).max() / want.std()
+        assert err < 3e-3, (cuts[:4], err, int(np.abs(got - want).max(axis=1).argmax()))
+    plain = ids.copy(); plain[455] = (mark + 2) % 90
+    assert np.abs(p.o.forward(plain)[461] - want[461]).max() / want.std() > 0.03      # ten times the budget above: the marked key is seen
+    p.close()
+
+
 def test_plain_kernels_agree_with_the_fast_ones():
     cfg = synth.gatuzen_config(**TINY)
     ids = np.random.default_rng(3).integers(0, cfg["vocab"], 300).astype(np.uint32)
