@@ -691,6 +691,18 @@ struct Engine final : SeqEngine {
     }
 };
 
+// segments for a recurrence whose longest entry is long (see recurrence.cuh): the longest segments that still give every SM four blocks
+inline void choose_segments(Engine& E, const StepView& v, Hgrn2Args& a) {
+    int longest = 0;
+    for (int e = 0; e < v.rb.E; ++e) longest = std::max(longest, v.h_ent_start[e + 1] - v.h_ent_start[e]);
+    if (longest >= kSegMinEntry && E.seg_state && E.opt.seq_impl == 0 && a.D <= 256) {
+        const int per_seg = a.H * ((a.Dv + kScanCols - 1) / kScanCols);
+        int L = kSegLen;
+        while (L < kSegLenMax && (longest / (2 * L)) * per_seg >= 4 * E.c.num_sms) L *= 2;
+        if (longest > L) { a.seg_state = E.seg_state; a.seg_decay = E.seg_decay; a.seg_len = L; a.seg_max = (longest + L - 1) / L; }
+    }
+}
+
 // ------------------------------------------------------------------------------------------------------------------------------
 struct Hgrn2Mixer final : Sublayer {
     Engine& E;
@@ -723,15 +735,7 @@ struct Hgrn2Mixer final : Sublayer {
         Hgrn2Args a{};
         a.qfv = E.proj; a.ld = in.N; a.lower = lower; a.norm_w = norm_w; a.eps = E.eps; a.state = state; a.slot_stride = slot_stride;
         a.out = E.inner; a.H = H; a.D = D; a.Dv = Dv; a.rb = v.rb;
-        int longest = 0;
-        for (int e = 0; e < v.rb.E; ++e) longest = std::max(longest, v.h_ent_start[e + 1] - v.h_ent_start[e]);
-        if (longest >= kSegMinEntry && E.seg_state && E.opt.seq_impl == 0) {      // long prompt portions: segments scanned side by side
-            // the longest segments that still give every SM four blocks: every segment costs a pass over the head's state
-            const int per_seg = H * ((Dv + kScanCols - 1) / kScanCols);
-            int L = kSegLen;
-            while (L < kSegLenMax && (longest / (2 * L)) * per_seg >= 4 * E.c.num_sms) L *= 2;
-            if (longest > L) { a.seg_state = E.seg_state; a.seg_decay = E.seg_decay; a.seg_len = L; a.seg_max = (longest + L - 1) / L; }
-        }
+        choose_segments(E, v, a);      // long prompt portions: segments scanned side by side
         E.tic("hgrn2 recurrence", 4.0 * T * H * D * Dv, 4.0 * T * (in.N + H * Dv) + 8.0 * v.rb.E * slot_stride);
         E.c.cnt.kernels += hgrn2_scan(E.c.stream, a, E.opt.seq_impl);
         E.toc();
@@ -869,19 +873,6 @@ struct DenseFF final : Sublayer {
     }
 };
 
-// segments for a recurrence whose longest entry is long (see recurrence.cuh): the longest segments that still give every SM four blocks
-inline void choose_segments(Engine& E, const StepView& v, Hgrn2Args& a, size_t slot_stride) {
-    (void)slot_stride;
-    int longest = 0;
-    for (int e = 0; e < v.rb.E; ++e) longest = std::max(longest, v.h_ent_start[e + 1] - v.h_ent_start[e]);
-    if (longest >= kSegMinEntry && E.seg_state && E.opt.seq_impl == 0 && a.D <= 256) {
-        const int per_seg = a.H * ((a.Dv + kScanCols - 1) / kScanCols);
-        int L = kSegLen;
-        while (L < kSegLenMax && (longest / (2 * L)) * per_seg >= 4 * E.c.num_sms) L *= 2;
-        if (longest > L) { a.seg_state = E.seg_state; a.seg_decay = E.seg_decay; a.seg_len = L; a.seg_max = (longest + L - 1) / L; }
-    }
-}
-
 // Gated linear attention: q = W_q h / sqrt(dim), k = W_k h, v = W_v h, a decay per key channel alpha = sigmoid(z)^(1 / tau) with
 // z = W_a2 (W_a1 h) + b (a low-rank projection); per head S <- diag(alpha) S + k v^T, o = S^T q; o is RMS-normed per head (gain over vdim
 // shared by the heads), multiplied by silu(W_g h) and projected by W_o.  The state is fp32 in the slot pool.
@@ -929,7 +920,7 @@ struct GlaMixer final : Sublayer {
         a.qfv = E.proj; a.ld = ld; a.q_off = 0; a.k_off = HD; a.f_off = z_off; a.v = E.proj; a.ld_v = ld; a.v_off = 2 * HD; a.gates_done = 1;
         a.norm_w = norm_w; a.eps = E.eps; a.out_gate = E.proj + 2 * HD + H * Dv; a.out_gate_ld = ld;
         a.state = state; a.slot_stride = slot_stride; a.out = E.inner; a.H = H; a.D = D; a.Dv = Dv; a.rb = v.rb;
-        choose_segments(E, v, a, slot_stride);
+        choose_segments(E, v, a);
         E.c.cnt.kernels += hgrn2_scan(E.c.stream, a, E.opt.seq_impl);
         E.toc();
         E.gemm(AEPI_STORE, E.inner, H * Dv, out, v.y, E.W, T);
@@ -996,7 +987,7 @@ struct Mamba2Mixer final : Sublayer {
         Hgrn2Args a{};
         a.qfv = E.proj; a.ld = ld; a.q_off = g.q_off; a.f_off = g.f_off; a.k_off = g.k_off; a.v = E.qbuf; a.ld_v = Cc; a.v_off = 0; a.gates_done = 1;
         a.norm_w = nullptr; a.eps = E.eps; a.state = state; a.slot_stride = slot_stride; a.out = E.inner; a.H = H; a.D = N; a.Dv = P; a.rb = v.rb;
-        choose_segments(E, v, a, slot_stride);
+        choose_segments(E, v, a);
         E.c.cnt.kernels += hgrn2_scan(st, a, E.opt.seq_impl);
         // (y + D x) * silu(z), RMS norm in groups, gain: in place
         GroupNormArgs n{};
